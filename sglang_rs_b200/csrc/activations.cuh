@@ -5,6 +5,8 @@
 //   SRB_ACT_SILU       g / (1 + exp(-g))                     (crates/sglang-kernel/src/cpu.rs:119-123)
 //   SRB_ACT_GELU_TANH  g/2 * (1 + tanh(sqrt(2/pi) * (g + 0.044715 g^3)))
 //   SRB_ACT_RELU2      max(g, 0)^2
+//   SRB_ACT_SWIGLU_CLAMP  g' sigmoid(1.702 g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); the
+//                      limit is the activation's parameter (`param`), which the other activations ignore
 //
 // A feed-forward without a gate calls the same function with u = 1.
 //
@@ -16,10 +18,17 @@
 #define SRB_ACT_SILU 0
 #define SRB_ACT_GELU_TANH 1
 #define SRB_ACT_RELU2 2
-#define SRB_ACT_COUNT 3
+#define SRB_ACT_SWIGLU_CLAMP 3
+#define SRB_ACT_COUNT 4
 
 template <bool EXACT>
-__device__ __forceinline__ float srb_gated(int activation, float g, float u) {
+__device__ __forceinline__ float srb_gated(int activation, float g, float u, float param = 0.f) {
+  if (activation == SRB_ACT_SWIGLU_CLAMP) {
+    g = fminf(g, param);
+    u = fminf(fmaxf(u, -param), param);
+    const float s = EXACT ? 1.0f / (1.0f + expf(-1.702f * g)) : __fdividef(1.0f, 1.0f + __expf(-1.702f * g));
+    return g * s * (u + 1.0f);
+  }
   if (activation == SRB_ACT_RELU2) {
     const float r = fmaxf(g, 0.f);
     return r * r * u;

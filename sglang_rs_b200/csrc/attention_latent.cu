@@ -43,6 +43,7 @@ struct LaParams {
   int* error_word;
   int table_stride, n_q, d, vd, page_size, num_pages;
   int split_size, max_splits;
+  int window;                  // a row sees itself and the window - 1 keys before it; 0: every earlier key
   int heads_per_block, rows_per_block, units_per_tile;
   float scale;
 };
@@ -82,8 +83,10 @@ latent_attention_kernel(LaParams p) {
     first_pos = p.positions[first_row];
     if (first_pos < 0) return;                      // a padding row
   }
-  const int lo = p.split_size == 0 ? 0 : split * p.split_size;
-  const int hi = p.split_size == 0 ? first_pos + n_rows : min(lo + p.split_size, first_pos + 1);
+  // the block's first row sees the earliest key of all its rows; splits are counted from that row's first split on
+  const int earliest = srb_first_visible(first_pos, p.window, 0);
+  const int lo = p.split_size == 0 ? earliest : max(earliest, (earliest / p.split_size + split) * p.split_size);
+  const int hi = p.split_size == 0 ? first_pos + n_rows : min((earliest / p.split_size + split + 1) * p.split_size, first_pos + 1);
   if (lo >= hi) return;
   const int hg = p.heads_per_block;
   const int head0 = group * hg;
@@ -106,6 +109,8 @@ latent_attention_kernel(LaParams p) {
   const bool valid_b = r_b < n_rows && head0 + m_b % hg < p.n_q;
   const int limit_a = valid_a ? min(hi - 1, first_pos + r_a) : -1;      // the last key the slot sees
   const int limit_b = valid_b ? min(hi - 1, first_pos + r_b) : -1;
+  const int from_a = valid_a ? max(lo, srb_first_visible(first_pos + r_a, p.window, 0)) : 0;   // the first key it sees
+  const int from_b = valid_b ? max(lo, srb_first_visible(first_pos + r_b, p.window, 0)) : 0;
   float max_a = -INFINITY, max_b = -INFINITY, sum_a = 0.f, sum_b = 0.f;
   const int cols_per_warp = vd / WARPS, nt = cols_per_warp / 8;
   float acc[NT_MAX][4];
@@ -172,7 +177,7 @@ latent_attention_kernel(LaParams p) {
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int key = base + warp * KEYS_PER_WARP + t * 8 + (lane & 3) * 2 + (c & 1);
-        const bool seen = key >= lo && key <= ((c >> 1) ? limit_b : limit_a);
+        const bool seen = key >= ((c >> 1) ? from_b : from_a) && key <= ((c >> 1) ? limit_b : limit_a);
         s[t][c] = seen ? s[t][c] * p.scale : -INFINITY;
         if (c >> 1) tile_max_b = fmaxf(tile_max_b, s[t][c]); else tile_max_a = fmaxf(tile_max_a, s[t][c]);
       }
@@ -299,11 +304,13 @@ static int launch_latent_attention(const LaParams& p, dim3 grid, size_t smem, cu
 
 // tiles null: rows are split rows (one block per row, head group and split; partial results merged by the generic
 // kernel's merge, scratch as there).  tiles given: prompt portions, unsplit (split_size is taken as 0).
-extern "C" int srb_latent_attention(const void* q, const void* pool, void* out, float* part_acc, float* part_ml,
-                                    const int* positions, const int* row_request, const int* block_table, int table_stride,
-                                    int rows, int n_q, int d, int vd, int page_size, int num_pages, int split_size,
-                                    int max_splits, const int* tiles, int num_tiles, float scale, const float* sinks,
-                                    int* error_word, void* stream) {
+// `window` > 0: a row sees itself and the window - 1 keys before it.
+extern "C" int srb_latent_attention_masked(const void* q, const void* pool, void* out, float* part_acc, float* part_ml,
+                                           const int* positions, const int* row_request, const int* block_table, int table_stride,
+                                           int rows, int n_q, int d, int vd, int page_size, int num_pages, int split_size,
+                                           int max_splits, const int* tiles, int num_tiles, float scale, const float* sinks,
+                                           int window, int* error_word, void* stream) {
+  if (window < 0) SRB_FAIL("latent_attention: a window of %d keys", window);
   if (!srb_latent_attention_supports(d, vd)) SRB_FAIL("latent_attention: rows of %d entries with values of %d are not taken", d, vd);
   if (n_q <= 0 || page_size <= 0 || num_pages <= 0 || table_stride <= 0) SRB_FAIL("latent_attention: sizes must be positive");
   LaParams p;
@@ -311,7 +318,7 @@ extern "C" int srb_latent_attention(const void* q, const void* pool, void* out, 
   p.part_acc = part_acc; p.part_ml = part_ml; p.positions = positions; p.row_request = row_request;
   p.block_table = block_table; p.tiles = tiles; p.sinks = sinks; p.error_word = error_word;
   p.table_stride = table_stride; p.n_q = n_q; p.d = d; p.vd = vd; p.page_size = page_size; p.num_pages = num_pages;
-  p.scale = scale;
+  p.scale = scale; p.window = window;
   p.heads_per_block = n_q < LA_SLOTS ? n_q : LA_SLOTS;
   const int groups = (n_q + p.heads_per_block - 1) / p.heads_per_block;
   dim3 grid;
@@ -343,9 +350,19 @@ extern "C" int srb_latent_attention(const void* q, const void* pool, void* out, 
   else status = launch_latent_attention<16, 4>(p, grid, smem, s);
   if (status != SRB_OK || tiles) return status;
   AttnParams m = {};
-  m.positions = positions; m.n_q = n_q; m.n_kv = 1; m.head_dim = d; m.window = 0; m.split_size = split_size;
+  m.positions = positions; m.n_q = n_q; m.n_kv = 1; m.head_dim = d; m.window = window; m.split_size = split_size;
   m.max_splits = max_splits; m.error_word = error_word; m.sinks = sinks; m.value_dim = vd;
   attention_combine_kernel<__nv_bfloat16><<<dim3(rows, n_q), 64, 0, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, m);
   SRB_LAUNCH_CHECK("attention_combine");
   return SRB_OK;
+}
+
+extern "C" int srb_latent_attention(const void* q, const void* pool, void* out, float* part_acc, float* part_ml,
+                                    const int* positions, const int* row_request, const int* block_table, int table_stride,
+                                    int rows, int n_q, int d, int vd, int page_size, int num_pages, int split_size,
+                                    int max_splits, const int* tiles, int num_tiles, float scale, const float* sinks,
+                                    int* error_word, void* stream) {
+  return srb_latent_attention_masked(q, pool, out, part_acc, part_ml, positions, row_request, block_table, table_stride, rows,
+                                     n_q, d, vd, page_size, num_pages, split_size, max_splits, tiles, num_tiles, scale, sinks, 0,
+                                     error_word, stream);
 }

@@ -303,11 +303,26 @@ struct NormSpec {
   const float* weight;
   const float* bias;
   float eps;
+  int groups;      // SRB_NORM_RMS only: the row is cut into this many equal consecutive parts, each divided by its own root mean square
+  float scale;     // multiplies the normalised values (1: as they are)
 };
 
 // normalises `v` (width floats in shared memory) in place; every thread of the block calls it
 __device__ __forceinline__ void norm_in_place(float* v, int width, const NormSpec& n, float* scratch) {
   if (n.kind == SRB_NORM_NONE) return;
+  if (n.kind == SRB_NORM_RMS && n.groups > 1) {
+    const int part = width / n.groups;
+    for (int g = 0; g < n.groups; ++g) {
+      float* u = v + g * part;
+      const float* w = n.weight + g * part;
+      float partial = 0.f;
+      for (int i = threadIdx.x; i < part; i += blockDim.x) partial += u[i] * u[i];
+      const float inv = 1.0f / sqrtf(srb_block_sum(partial, scratch) / (float)part + n.eps);
+      for (int i = threadIdx.x; i < part; i += blockDim.x) u[i] = u[i] * inv * w[i] * n.scale;
+    }
+    __syncthreads();
+    return;
+  }
   float mean = 0.f;
   if (n.kind == SRB_NORM_LAYER) {
     float partial = 0.f;
@@ -323,7 +338,7 @@ __device__ __forceinline__ void norm_in_place(float* v, int width, const NormSpe
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float y = (v[i] - mean) * inv * n.weight[i];
     if (n.kind == SRB_NORM_LAYER && n.bias) y += n.bias[i];
-    v[i] = y;
+    v[i] = y * n.scale;
   }
   __syncthreads();
 }
@@ -361,12 +376,18 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[width + i] = srb_from_float<T>(extra[src + i]);
 }
 
-extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float* delta_f32, int inner_kind,
-                                 const float* inner_weight, const float* inner_bias, float inner_eps, int outer_kind,
-                                 const float* outer_weight, const float* outer_bias, float outer_eps, void* out,
-                                 long long out_pitch, const float* extra, const int* row_index, int rows, int width,
-                                 int write_residual, int dtype, void* stream) {
+// `*_groups` (RMS norms only; 1: the whole row) and `*_scale` (1: none) as NormSpec says
+extern "C" int srb_norm_add_norm_ex(float* residual, const void* delta, const float* delta_f32, int inner_kind,
+                                    const float* inner_weight, const float* inner_bias, float inner_eps, int inner_groups,
+                                    float inner_scale, int outer_kind, const float* outer_weight, const float* outer_bias,
+                                    float outer_eps, int outer_groups, float outer_scale, void* out, long long out_pitch,
+                                    const float* extra, const int* row_index, int rows, int width, int write_residual,
+                                    int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
+  for (int groups : {inner_groups, outer_groups})
+    if (groups < 1 || width % groups) SRB_FAIL("norm_add_norm: a row of %d entries does not split into %d equal parts", width, groups);
+  if ((inner_groups > 1 && inner_kind != SRB_NORM_RMS) || (outer_groups > 1 && outer_kind != SRB_NORM_RMS))
+    SRB_FAIL("norm_add_norm: only an RMS norm is taken in parts");
   if (width <= 0) SRB_FAIL("norm_add_norm: width %d must be positive", width);
   for (int kind : {inner_kind, outer_kind})
     if (kind < SRB_NORM_NONE || kind > SRB_NORM_LAYER) SRB_FAIL("norm_add_norm: unknown kind of norm %d", kind);
@@ -376,7 +397,8 @@ extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float
   if (out && out_pitch < (long long)width * (extra ? 2 : 1)) SRB_FAIL("norm_add_norm: rows of the output overlap");
   const size_t smem = (size_t)(width + 33) * sizeof(float);
   if (smem > 227 * 1024) SRB_FAIL("norm_add_norm: width %d needs %zu bytes of shared memory (limit 232448)", width, smem);
-  const NormSpec inner{inner_kind, inner_weight, inner_bias, inner_eps}, outer{outer_kind, outer_weight, outer_bias, outer_eps};
+  const NormSpec inner{inner_kind, inner_weight, inner_bias, inner_eps, inner_groups, inner_scale};
+  const NormSpec outer{outer_kind, outer_weight, outer_bias, outer_eps, outer_groups, outer_scale};
   const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32) {
@@ -396,6 +418,113 @@ extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float
     SRB_FAIL("norm_add_norm: unknown dtype %d", dtype);
   }
   SRB_LAUNCH_CHECK("norm_add_norm");
+  return SRB_OK;
+}
+
+extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float* delta_f32, int inner_kind,
+                                 const float* inner_weight, const float* inner_bias, float inner_eps, int outer_kind,
+                                 const float* outer_weight, const float* outer_bias, float outer_eps, void* out,
+                                 long long out_pitch, const float* extra, const int* row_index, int rows, int width,
+                                 int write_residual, int dtype, void* stream) {
+  return srb_norm_add_norm_ex(residual, delta, delta_f32, inner_kind, inner_weight, inner_bias, inner_eps, 1, 1.0f, outer_kind,
+                              outer_weight, outer_bias, outer_eps, 1, 1.0f, out, out_pitch, extra, row_index, rows, width,
+                              write_residual, dtype, stream);
+}
+
+// ---- two sublayers that read one norm: the residual sum of both, scaled ------------------------------
+// residual += mult * (a + b), in 32-bit.  a: T [rows, width] (`a`), float (`a_f32`, `a_parts` tensors `a_part_stride`
+// floats apart, added in order: partial sums of a product cut along K), or neither; b: float [rows, width] or null.
+// `rounded` (optional, T [rows, width]) receives the new residual rounded: the input of a product that reads the stream.
+template <typename T>
+__global__ void scaled_sum_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ a_f32,
+                                  int a_parts, size_t a_part_stride, const float* __restrict__ b, float mult,
+                                  T* __restrict__ rounded, size_t total) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    float y = 0.f;
+    if (a) y = srb_to_float(a[idx]);
+    for (int part = 0; part < a_parts; ++part) y += a_f32[part * a_part_stride + idx];
+    if (b) y += b[idx];
+    const float x = fmaf(mult, y, residual[idx]);
+    residual[idx] = x;
+    if (rounded) rounded[idx] = srb_from_float<T>(x);
+  }
+}
+
+extern "C" int srb_scaled_sum(float* residual, const void* a, const float* a_f32, int a_parts, long long a_part_stride,
+                              const float* b, float mult, void* rounded, int rows, int width, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0) SRB_FAIL("scaled_sum: width %d must be positive", width);
+  if (a_parts < 0 || (a_parts > 0 && !a_f32)) SRB_FAIL("scaled_sum: partial sums are missing");
+  const size_t total = (size_t)rows * width;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int grid = elementwise_grid(total, 256);
+  if (dtype == SRB_DTYPE_F32)
+    SRB_CUDA_CALL(srb_launch(scaled_sum_kernel<float>, dim3(grid), dim3(256), 0, s, residual, (const float*)a, a_f32, a_parts,
+                             (size_t)a_part_stride, b, mult, (float*)rounded, total));
+  else if (dtype == SRB_DTYPE_BF16)
+    SRB_CUDA_CALL(srb_launch(scaled_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, residual, (const __nv_bfloat16*)a,
+                             a_f32, a_parts, (size_t)a_part_stride, b, mult, (__nv_bfloat16*)rounded, total));
+  else
+    SRB_FAIL("scaled_sum: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("scaled_sum");
+  return SRB_OK;
+}
+
+// ---- a gate that a table's row, chosen by the token, multiplies --------------------------------------
+// out[r, j] = act(gate[r, j]) * table[ids[r], offset + j], j < dim; table rows are `table_pitch` entries long.
+template <typename T>
+__global__ void token_gate_kernel(const T* __restrict__ gate, const int* __restrict__ ids, const T* __restrict__ table,
+                                  size_t table_pitch, int offset, int vocab, int dim, int activation, T* __restrict__ out,
+                                  int* __restrict__ error_word) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_TOKEN);
+    for (int j = threadIdx.x; j < dim; j += blockDim.x) out[(size_t)row * dim + j] = srb_from_float<T>(0.f);
+    return;
+  }
+  const T* e = table + (size_t)id * table_pitch + offset;
+  for (int j = threadIdx.x; j < dim; j += blockDim.x)
+    out[(size_t)row * dim + j] = srb_from_float<T>(srb_gated<true>(activation, srb_to_float(gate[(size_t)row * dim + j]), srb_to_float(e[j])));
+}
+
+extern "C" int srb_token_gate(const void* gate, const int* ids, const void* table, long long table_pitch, int offset, int vocab,
+                              int rows, int dim, int activation, void* out, int* error_word, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (dim <= 0 || offset < 0 || offset + dim > table_pitch || vocab <= 0) SRB_FAIL("token_gate: %d entries from %d do not fit rows of %lld", dim, offset, table_pitch);
+  if (activation < 0 || activation >= SRB_ACT_COUNT || activation == SRB_ACT_SWIGLU_CLAMP) SRB_FAIL("token_gate: activation %d is not taken", activation);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int block = dim >= 256 ? 256 : (dim >= 64 ? 64 : 32);
+  if (dtype == SRB_DTYPE_F32)
+    SRB_CUDA_CALL(srb_launch(token_gate_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)gate, ids, (const float*)table,
+                             (size_t)table_pitch, offset, vocab, dim, activation, (float*)out, error_word));
+  else if (dtype == SRB_DTYPE_BF16)
+    SRB_CUDA_CALL(srb_launch(token_gate_kernel<__nv_bfloat16>, dim3(rows), dim3(block), 0, s, (const __nv_bfloat16*)gate, ids,
+                             (const __nv_bfloat16*)table, (size_t)table_pitch, offset, vocab, dim, activation,
+                             (__nv_bfloat16*)out, error_word));
+  else
+    SRB_FAIL("token_gate: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("token_gate");
+  return SRB_OK;
+}
+
+// values *= factor (32-bit, in place): a model's constant on its logits
+__global__ void scale_values_kernel(float* __restrict__ values, float factor, size_t total) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    values[idx] *= factor;
+}
+
+extern "C" int srb_scale_values(float* values, long long total, float factor, void* stream) {
+  if (total <= 0) return SRB_OK;
+  SRB_CUDA_CALL(srb_launch(scale_values_kernel, dim3(elementwise_grid((size_t)total, 256)), dim3(256), 0, (cudaStream_t)stream,
+                           values, factor, (size_t)total));
+  SRB_LAUNCH_CHECK("scale_values");
   return SRB_OK;
 }
 

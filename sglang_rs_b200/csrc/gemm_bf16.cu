@@ -59,6 +59,7 @@ struct GemmArgs {
   int ldo;                   // row pitch of out, in elements
   int up_row_offset;         // EPI_SILU: rows of the up matrix start here in W
   int activation;            // EPI_SILU: which SRB_ACT_* is applied to the gate half
+  float act_param;           // the activation's parameter (a limit), for those that have one
   int k_blocks_per_split;
   int* error_word;
   // Grouped products (routed experts): `plan` (device) = [number of tiles, first slot of every expert (experts + 1),
@@ -236,7 +237,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             if (token >= token_limit) break;
             const float g = acc[j], u = exchange[((quarter & 1) * 32 + lane) * 16 + j];
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
-                __float2bfloat16_rn(srb_gated<true>(args.activation, g, u));
+                __float2bfloat16_rn(srb_gated<true>(args.activation, g, u, args.act_param));
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");       // the buffer is reused by the next 16 tokens
@@ -253,7 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] = __float2bfloat16_rn(acc[j]);
           } else if (EPI == EPI_ACT) {
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
-                __float2bfloat16_rn(srb_gated<true>(args.activation, acc[j], 1.0f));
+                __float2bfloat16_rn(srb_gated<true>(args.activation, acc[j], 1.0f, args.act_param));
           } else if (EPI == EPI_F32) {
             reinterpret_cast<float*>(args.out)[(size_t)token * args.ldo + feature] = acc[j];
           } else {
@@ -388,6 +389,8 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
   if (mode < 0 || mode > 5) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
   if ((mode == EPI_SILU || mode == EPI_ACT) && (activation < 0 || activation >= SRB_ACT_COUNT))
     SRB_FAIL("gemm_bf16: unknown activation %d", activation);
+  if ((mode == EPI_SILU || mode == EPI_ACT) && activation == SRB_ACT_SWIGLU_CLAMP)
+    SRB_FAIL("gemm_bf16: an activation with a parameter is taken by the grouped mode only");
   if (ldo < features) SRB_FAIL("gemm_bf16: output pitch %d is smaller than %d features", ldo, features);
   if (mode == EPI_SILU && up_row_offset + features > rows_of_w)
     SRB_FAIL("gemm_bf16: the up rows %d..%d lie outside the %d rows of w", up_row_offset, up_row_offset + features,
@@ -408,6 +411,7 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
   GemmArgs args;
   args.out = out; args.tokens = tokens; args.features = features; args.k = k; args.ldo = ldo;
   args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
+  args.act_param = 0.f;
   args.plan = nullptr; args.experts = 0; args.expert_rows = 0;
   args.k_blocks_per_split = (total_k_blocks + splits - 1) / splits;
   const int used_splits = (total_k_blocks + args.k_blocks_per_split - 1) / args.k_blocks_per_split;
@@ -448,7 +452,7 @@ static int launch_grouped(const CUtensorMap& map_w, const CUtensorMap& map_x, co
 
 extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, const int* plan, int max_tiles, int tile_slots,
                                      int slots, int experts, int expert_rows, int features, int k, int ldo,
-                                     int up_row_offset, int mode, int activation, int* error_word, void* stream) {
+                                     int up_row_offset, int mode, int activation, float act_param, int* error_word, void* stream) {
   if (slots <= 0 || features <= 0 || max_tiles <= 0) return SRB_OK;
   if (tile_slots != 128 && tile_slots != 256) SRB_FAIL("gemm_bf16_grouped: tiles of %d slots are not 128 or 256", tile_slots);
   if (k <= 0 || k % 8 != 0) SRB_FAIL("gemm_bf16_grouped: inner size %d must be a positive multiple of 8", k);
@@ -467,6 +471,7 @@ extern "C" int srb_gemm_bf16_grouped(const void* x, const void* w, void* out, co
   GemmArgs args;
   args.out = out; args.tokens = slots; args.features = features; args.k = k; args.ldo = ldo;
   args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
+  args.act_param = act_param;
   args.plan = plan; args.experts = experts; args.expert_rows = expert_rows;
   args.k_blocks_per_split = (k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
   cudaStream_t s = (cudaStream_t)stream;

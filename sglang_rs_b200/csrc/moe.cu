@@ -36,11 +36,75 @@ static inline int moe_tile_rows(int rows, int top, int experts) {
 #define MOE_K 16
 #define MOE_MAX_EXPERTS 1024
 
+// How the router's logits become a choice and weights.  `scoring` 0: scores are a softmax over all experts; 1: each
+// expert's score is the sigmoid of its logit.  `choice_bias` (one float per expert, or null) is added to the scores for
+// the choice only; the weights are the chosen experts' scores without it, divided by their sum plus `norm_eps` if
+// `renormalize`, then multiplied by `scale`.
+struct RouteRule {
+  int scoring;
+  int renormalize;
+  const float* choice_bias;
+  float scale;
+  float norm_eps;
+};
+#define MOE_SCORE_SOFTMAX 0
+#define MOE_SCORE_SIGMOID 1
+
+// One warp.  `score` holds the row's logits on entry; `pick` is scratch of the same length.  The `top` experts with
+// the largest choice scores are taken (ties: the lower index).
+__device__ __forceinline__ void moe_choose(float* score, float* pick, int experts, int top, const RouteRule& rule, int lane,
+                                           int* __restrict__ chosen, float* __restrict__ weights) {
+  float sum = 1.f;
+  if (rule.scoring == MOE_SCORE_SIGMOID) {
+    for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
+  } else {
+    float top_logit = -INFINITY;
+    for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, score[e]);
+    top_logit = srb_warp_max(top_logit);
+    sum = 0.f;
+    for (int e = lane; e < experts; e += 32) {
+      const float p = expf(score[e] - top_logit);
+      score[e] = p;
+      sum += p;
+    }
+    sum = srb_warp_sum(sum);
+  }
+  for (int e = lane; e < experts; e += 32) pick[e] = rule.choice_bias ? score[e] / sum + rule.choice_bias[e] : score[e];
+  __syncwarp();
+  float kept = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_index = experts;
+    for (int e = lane; e < experts; e += 32)
+      if (pick[e] > best) { best = pick[e]; best_index = e; }          // the first of equals within a lane
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+      if (other > best || (other == best && other_index < best_index)) { best = other; best_index = other_index; }
+    }
+    if (best_index >= experts) best_index = 0;                          // only if every score left is not a number
+    const float weight = score[best_index] / sum;
+    if (lane == 0) {
+      chosen[k] = best_index;
+      weights[k] = weight;
+      pick[best_index] = -INFINITY;                                     // never chosen again
+    }
+    kept += weight;
+    __syncwarp();
+  }
+  if (lane < top) {
+    float w = weights[lane];
+    if (rule.renormalize) w /= kept + rule.norm_eps;
+    weights[lane] = w * rule.scale;
+  }
+}
+
 // One block per row.  Warps share the experts' dot products; warp 0 then picks the largest scores.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const T* __restrict__ router, int width, int experts, int top,
-                                 int renormalize, int* __restrict__ chosen, float* __restrict__ weights) {
+                                 RouteRule rule, int* __restrict__ chosen, float* __restrict__ weights) {
   __shared__ float score[MOE_MAX_EXPERTS];
+  __shared__ float pick[MOE_MAX_EXPERTS];
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -82,42 +146,15 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const T* __restrict__ 
   }
   __syncthreads();
   if (warp != 0) return;
-  float top_logit = -INFINITY;
-  for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, score[e]);
-  top_logit = srb_warp_max(top_logit);
-  float sum = 0.f;
-  for (int e = lane; e < experts; e += 32) {
-    const float p = expf(score[e] - top_logit);
-    score[e] = p;
-    sum += p;
-  }
-  sum = srb_warp_sum(sum);
-  __syncwarp();
-  float kept = 0.f;
-  for (int k = 0; k < top; ++k) {
-    float best = -1.f;
-    int best_index = experts;
-    for (int e = lane; e < experts; e += 32)
-      if (score[e] > best) { best = score[e]; best_index = e; }          // the first of equals within a lane
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
-      const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
-      if (other > best || (other == best && other_index < best_index)) { best = other; best_index = other_index; }
-    }
-    if (lane == 0) {
-      chosen[(size_t)row * top + k] = best_index;
-      weights[(size_t)row * top + k] = best / sum;
-      score[best_index] = -1.f;                                           // scores are positive: never chosen again
-    }
-    kept += best / sum;
-    __syncwarp();
-  }
-  if (renormalize && lane < top) weights[(size_t)row * top + lane] /= kept;
+  moe_choose(score, pick, experts, top, rule, lane, chosen + (size_t)row * top, weights + (size_t)row * top);
 }
 
-extern "C" int srb_moe_route(const void* h, const void* router, int rows, int width, int experts, int top, int renormalize,
-                             int* chosen, float* weights, int dtype, void* stream) {
+extern "C" int srb_moe_route_ex(const void* h, const void* router, int rows, int width, int experts, int top, int renormalize,
+                                int scoring, const float* choice_bias, float scale, float norm_eps, int* chosen, float* weights,
+                                int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
+  if (scoring != MOE_SCORE_SOFTMAX && scoring != MOE_SCORE_SIGMOID) SRB_FAIL("moe_route: unknown scoring %d", scoring);
+  const RouteRule rule{scoring, renormalize, choice_bias, scale, norm_eps};
   if (experts <= 0 || experts > MOE_MAX_EXPERTS) SRB_FAIL("moe_route: %d experts are outside 1 .. %d", experts, MOE_MAX_EXPERTS);
   if (top <= 0 || top > experts || top > 32) SRB_FAIL("moe_route: %d chosen experts are outside 1 .. min(%d, 32)", top, experts);
   if (width <= 0) SRB_FAIL("moe_route: width %d must be positive", width);
@@ -125,72 +162,58 @@ extern "C" int srb_moe_route(const void* h, const void* router, int rows, int wi
   const int block = experts >= 32 ? 1024 : 32 * experts;          // a warp per expert, up to 32 warps
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(moe_route_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)h, (const float*)router,
-                             width, experts, top, renormalize, chosen, weights));
+                             width, experts, top, rule, chosen, weights));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(moe_route_kernel<__nv_bfloat16>, dim3(rows), dim3(block), 0, s, (const __nv_bfloat16*)h,
-                             (const __nv_bfloat16*)router, width, experts, top, renormalize, chosen, weights));
+                             (const __nv_bfloat16*)router, width, experts, top, rule, chosen, weights));
   else
     SRB_FAIL("moe_route: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("moe_route");
   return SRB_OK;
 }
 
+extern "C" int srb_moe_route(const void* h, const void* router, int rows, int width, int experts, int top, int renormalize,
+                             int* chosen, float* weights, int dtype, void* stream) {
+  return srb_moe_route_ex(h, router, rows, width, experts, top, renormalize, MOE_SCORE_SOFTMAX, nullptr, 1.0f, 0.0f, chosen,
+                          weights, dtype, stream);
+}
+
 // The choice alone, from logits that a product kernel made (float [rows, experts], `pitch` floats apart): a warp per
 // row does the softmax over all experts and picks the `top` largest as moe_route_kernel does.
 __global__ void moe_select_kernel(const float* __restrict__ logits, size_t pitch, int rows, int experts, int top,
-                                  int renormalize, int* __restrict__ chosen, float* __restrict__ weights) {
-  extern __shared__ float select_scores[];                  // [warps of the block][experts]
+                                  RouteRule rule, int* __restrict__ chosen, float* __restrict__ weights) {
+  extern __shared__ float select_scores[];                  // [warps of the block][2][experts]
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   if (row >= rows) return;
-  float* score = select_scores + (size_t)warp * experts;
+  float* score = select_scores + (size_t)warp * 2 * experts;
   const float* z = logits + (size_t)row * pitch;
-  float top_logit = -INFINITY;
-  for (int e = lane; e < experts; e += 32) top_logit = fmaxf(top_logit, z[e]);
-  top_logit = srb_warp_max(top_logit);
-  float sum = 0.f;
-  for (int e = lane; e < experts; e += 32) {
-    const float p = expf(z[e] - top_logit);
-    score[e] = p;
-    sum += p;
-  }
-  sum = srb_warp_sum(sum);
-  __syncwarp();
-  float kept = 0.f;
-  for (int k = 0; k < top; ++k) {
-    float best = -1.f;
-    int best_index = experts;
-    for (int e = lane; e < experts; e += 32)
-      if (score[e] > best) { best = score[e]; best_index = e; }
-    for (int offset = 16; offset > 0; offset >>= 1) {
-      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
-      const int other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
-      if (other > best || (other == best && other_index < best_index)) { best = other; best_index = other_index; }
-    }
-    if (lane == 0) {
-      chosen[(size_t)row * top + k] = best_index;
-      weights[(size_t)row * top + k] = best / sum;
-      score[best_index] = -1.f;
-    }
-    kept += best / sum;
-    __syncwarp();
-  }
-  if (renormalize && lane < top) weights[(size_t)row * top + lane] /= kept;
+  for (int e = lane; e < experts; e += 32) score[e] = z[e];
+  moe_choose(score, score + experts, experts, top, rule, lane, chosen + (size_t)row * top, weights + (size_t)row * top);
 }
 
-extern "C" int srb_moe_select(const float* logits, long long pitch, int rows, int experts, int top, int renormalize,
-                              int* chosen, float* weights, void* stream) {
+extern "C" int srb_moe_select_ex(const float* logits, long long pitch, int rows, int experts, int top, int renormalize,
+                                 int scoring, const float* choice_bias, float scale, float norm_eps, int* chosen,
+                                 float* weights, void* stream) {
   if (rows <= 0) return SRB_OK;
+  if (scoring != MOE_SCORE_SOFTMAX && scoring != MOE_SCORE_SIGMOID) SRB_FAIL("moe_select: unknown scoring %d", scoring);
+  const RouteRule rule{scoring, renormalize, choice_bias, scale, norm_eps};
   if (experts <= 0 || experts > MOE_MAX_EXPERTS) SRB_FAIL("moe_select: %d experts are outside 1 .. %d", experts, MOE_MAX_EXPERTS);
   if (top <= 0 || top > experts || top > 32) SRB_FAIL("moe_select: %d chosen experts are outside 1 .. min(%d, 32)", top, experts);
   if (pitch < experts) SRB_FAIL("moe_select: rows of the logits overlap");
   const int warps = 4;
-  SRB_CUDA_CALL(srb_launch(moe_select_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), (size_t)warps * experts * 4,
-                           (cudaStream_t)stream, logits, (size_t)pitch, rows, experts, top, renormalize, chosen, weights));
+  SRB_CUDA_CALL(srb_launch(moe_select_kernel, dim3((rows + warps - 1) / warps), dim3(32 * warps), (size_t)warps * experts * 8,
+                           (cudaStream_t)stream, logits, (size_t)pitch, rows, experts, top, rule, chosen, weights));
   SRB_LAUNCH_CHECK("moe_select");
   return SRB_OK;
+}
+
+extern "C" int srb_moe_select(const float* logits, long long pitch, int rows, int experts, int top, int renormalize,
+                              int* chosen, float* weights, void* stream) {
+  return srb_moe_select_ex(logits, pitch, rows, experts, top, renormalize, MOE_SCORE_SOFTMAX, nullptr, 1.0f, 0.0f, chosen,
+                           weights, stream);
 }
 
 // One block.  plan: [0] number of tiles, then offsets[experts + 1], then per tile (expert, first slot).
@@ -294,7 +317,7 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* __restrict__ w_b,
                    const int* __restrict__ plan, const int* __restrict__ slot_row, int experts, int n_in, int n_out,
-                   int activation, T* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
+                   int activation, float act_param, T* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
   constexpr bool GATED = MODE == MOE_GATED, GATHER = MODE != MOE_DOWN;
   __shared__ float x_tile[MOE_K][MOE_TILE + 4];
   __shared__ float a_tile[MOE_K][MOE_TILE + 4];
@@ -358,9 +381,9 @@ moe_product_kernel(const T* __restrict__ x, const T* __restrict__ w_a, const T* 
       const int c = col0 + tx * 4 + j;
       if (c >= n_out) continue;
       if (GATED)
-        out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], acc_b[i][j]));
+        out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], acc_b[i][j], act_param));
       else if (MODE == MOE_ACT)
-        out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], 1.0f));
+        out_t[slot * n_out + c] = srb_from_float<T>(srb_gated<true>(activation, acc_a[i][j], 1.0f, act_param));
       else
         out_f[slot * n_out + c] = acc_a[i][j];
     }
@@ -372,7 +395,7 @@ template <int MODE>
 __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                        const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
-                       const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
+                       const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation, float act_param,
                        __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, int tile_rows, size_t expert_stride) {
   constexpr bool GATED = MODE == MOE_GATED, GATHER = MODE != MOE_DOWN;
   __shared__ __align__(16) TileMmaSmem s;
@@ -409,9 +432,9 @@ moe_product_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
         if (r >= count || col >= n_out) continue;
         const size_t at = ((size_t)first + r) * n_out + col;
         if (GATED)
-          out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], acc[NW - 1][i][j][c]));
+          out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], acc[NW - 1][i][j][c], act_param));
         else if (MODE == MOE_ACT)
-          out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], 1.0f));
+          out_t[at] = __float2bfloat16_rn(srb_gated<true>(activation, acc[0][i][j][c], 1.0f, act_param));
         else
           out_f[at] = acc[0][i][j][c];
       }
@@ -423,7 +446,7 @@ template <int MODE, int ROWS, int STAGES>
 __global__ void __launch_bounds__(256)
 moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w_a,
                          const __nv_bfloat16* __restrict__ w_b, const int* __restrict__ plan,
-                         const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation,
+                         const int* __restrict__ slot_row, int experts, int n_in, int n_out, int activation, float act_param,
                          __nv_bfloat16* __restrict__ out_t, float* __restrict__ out_f, size_t expert_stride) {
   constexpr bool GATED = MODE == MOE_GATED, GATHER = MODE != MOE_DOWN;
   constexpr int NW = GATED ? 2 : 1;
@@ -461,8 +484,8 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         const size_t at = ((size_t)first + r) * n_out + col;
         const bool pair = col + 1 < n_out;
         if (MODE != MOE_DOWN) {
-          const float lo = srb_gated<true>(activation, acc[0][i][j][c], GATED ? acc[NW - 1][i][j][c] : 1.0f);
-          const float hi = srb_gated<true>(activation, acc[0][i][j][c + 1], GATED ? acc[NW - 1][i][j][c + 1] : 1.0f);
+          const float lo = srb_gated<true>(activation, acc[0][i][j][c], GATED ? acc[NW - 1][i][j][c] : 1.0f, act_param);
+          const float hi = srb_gated<true>(activation, acc[0][i][j][c + 1], GATED ? acc[NW - 1][i][j][c + 1] : 1.0f, act_param);
           if (pair && (at & 1) == 0) {
             *reinterpret_cast<unsigned*>(out_t + at) = pack_bf16(lo, hi);
           } else {
@@ -480,7 +503,7 @@ moe_product_async_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 
 template <typename T>
 static int launch_moe_products(int mode, const void* x, const void* w_a, const void* w_b, const int* plan,
-                               const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation,
+                               const int* slot_row, int rows, int top, int experts, int n_in, int n_out, int activation, float act_param,
                                void* out_t, float* out_f, size_t expert_stride, cudaStream_t s) {
   const int tile_rows = moe_tile_rows(rows, top, experts);
   dim3 grid((n_out + MOE_TILE - 1) / MOE_TILE, srb_moe_max_tiles(rows, top, experts), (tile_rows + MOE_TILE - 1) / MOE_TILE);
@@ -495,7 +518,7 @@ static int launch_moe_products(int mode, const void* x, const void* w_a, const v
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                       \
     SRB_CUDA_CALL(srb_launch(moe_product_async_kernel<MODE, ROWS, STAGES>, grid, dim3(256), smem, s,                   \
                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan,      \
-                             slot_row, experts, n_in, n_out, activation, (__nv_bfloat16*)out_t, out_f, expert_stride)); \
+                             slot_row, experts, n_in, n_out, activation, act_param, (__nv_bfloat16*)out_t, out_f, expert_stride)); \
   } while (0)
     if (tile_rows == MOE_FEW_ROWS) {
       if (mode == MOE_GATED) MOE_ASYNC_LAUNCH(MOE_GATED, MOE_FEW_ROWS, MOE_FEW_STAGES);
@@ -515,7 +538,7 @@ static int launch_moe_products(int mode, const void* x, const void* w_a, const v
 #define MOE_MMA_LAUNCH(MODE)                                                                                             \
   SRB_CUDA_CALL(srb_launch(moe_product_mma_kernel<MODE>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,                 \
                            (const __nv_bfloat16*)w_a, (const __nv_bfloat16*)w_b, plan, slot_row, experts, n_in, n_out,   \
-                           activation, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride))
+                           activation, act_param, (__nv_bfloat16*)out_t, out_f, tile_rows, expert_stride))
     if (mode == MOE_GATED) MOE_MMA_LAUNCH(MOE_GATED);
     else if (mode == MOE_ACT) MOE_MMA_LAUNCH(MOE_ACT);
     else MOE_MMA_LAUNCH(MOE_DOWN);
@@ -525,7 +548,7 @@ static int launch_moe_products(int mode, const void* x, const void* w_a, const v
   }
 #define MOE_PLAIN_LAUNCH(MODE)                                                                                           \
   SRB_CUDA_CALL(srb_launch(moe_product_kernel<T, MODE>, grid, dim3(256), 0, s, (const T*)x, (const T*)w_a, (const T*)w_b, \
-                           plan, slot_row, experts, n_in, n_out, activation, (T*)out_t, out_f, tile_rows, expert_stride))
+                           plan, slot_row, experts, n_in, n_out, activation, act_param, (T*)out_t, out_f, tile_rows, expert_stride))
   if (mode == MOE_GATED) MOE_PLAIN_LAUNCH(MOE_GATED);
   else if (mode == MOE_ACT) MOE_PLAIN_LAUNCH(MOE_ACT);
   else MOE_PLAIN_LAUNCH(MOE_DOWN);
@@ -537,31 +560,31 @@ static int launch_moe_products(int mode, const void* x, const void* w_a, const v
 // h: [rows, width]; w_gate, w_up: expert e's [inner, width] matrix starts expert_stride elements after expert e - 1's
 // (the two may be halves of one stacked tensor); act: [rows * top, inner]
 extern "C" int srb_moe_gated_up(const void* h, const void* w_gate, const void* w_up, long long expert_stride, const int* plan,
-                                const int* slot_row, int rows, int top, int experts, int width, int inner, int activation,
+                                const int* slot_row, int rows, int top, int experts, int width, int inner, int activation, float act_param,
                                 void* act, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (width <= 0 || inner <= 0) SRB_FAIL("moe_gated_up: sizes %d, %d must be positive", width, inner);
   if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("moe_gated_up: unknown activation %d", activation);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(MOE_GATED, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
+    return launch_moe_products<float>(MOE_GATED, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act_param, act, nullptr, (size_t)expert_stride, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(MOE_GATED, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, (size_t)expert_stride, s);
+    return launch_moe_products<__nv_bfloat16>(MOE_GATED, h, w_gate, w_up, plan, slot_row, rows, top, experts, width, inner, activation, act_param, act, nullptr, (size_t)expert_stride, s);
   SRB_FAIL("moe_gated_up: unknown dtype %d", dtype);
 }
 
 // The first product of experts without a gate: act[slot, :] = activation(W_up[e] h[row]); w_up: [experts, inner, width].
 extern "C" int srb_moe_act_up(const void* h, const void* w_up, const int* plan, const int* slot_row, int rows, int top,
-                              int experts, int width, int inner, int activation, void* act, int dtype, void* stream) {
+                              int experts, int width, int inner, int activation, float act_param, void* act, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (width <= 0 || inner <= 0) SRB_FAIL("moe_act_up: sizes %d, %d must be positive", width, inner);
   if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("moe_act_up: unknown activation %d", activation);
   cudaStream_t s = (cudaStream_t)stream;
   const size_t stride = (size_t)inner * width;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(MOE_ACT, h, w_up, nullptr, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, stride, s);
+    return launch_moe_products<float>(MOE_ACT, h, w_up, nullptr, plan, slot_row, rows, top, experts, width, inner, activation, act_param, act, nullptr, stride, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(MOE_ACT, h, w_up, nullptr, plan, slot_row, rows, top, experts, width, inner, activation, act, nullptr, stride, s);
+    return launch_moe_products<__nv_bfloat16>(MOE_ACT, h, w_up, nullptr, plan, slot_row, rows, top, experts, width, inner, activation, act_param, act, nullptr, stride, s);
   SRB_FAIL("moe_act_up: unknown dtype %d", dtype);
 }
 
@@ -572,9 +595,9 @@ extern "C" int srb_moe_down(const void* act, const void* w_down, const int* plan
   if (width <= 0 || inner <= 0) SRB_FAIL("moe_down: sizes %d, %d must be positive", width, inner);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_moe_products<float>(MOE_DOWN, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
+    return launch_moe_products<float>(MOE_DOWN, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, 0.f, nullptr, y, (size_t)width * inner, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_moe_products<__nv_bfloat16>(MOE_DOWN, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, nullptr, y, (size_t)width * inner, s);
+    return launch_moe_products<__nv_bfloat16>(MOE_DOWN, act, w_down, nullptr, plan, nullptr, rows, top, experts, inner, width, 0, 0.f, nullptr, y, (size_t)width * inner, s);
   SRB_FAIL("moe_down: unknown dtype %d", dtype);
 }
 

@@ -215,23 +215,27 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
 
     ``inner`` and ``outer`` are ``(kind, weight, bias, eps)`` with kind one of ``NORM_KINDS`` (``none``: the
     identity; ``rms``: v / sqrt(mean(v^2) + eps) * w; ``layer``: (v - mean) / sqrt(var + eps) * w + b) or None
-    for the identity.  ``delta`` is [rows, width] of ``out``'s dtype or float32, or None (x is the residual).
+    for the identity.  A spec may go on with ``(..., groups, scale)``: an RMS norm taken in ``groups`` equal
+    consecutive parts of the row, each with its own mean, and a factor on the normalised values.  ``delta`` is [rows, width] of ``out``'s dtype or float32, or None (x is the residual).
     ``out`` may be None (only the sum is wanted) and may have rows longer than ``width``; with ``extra``
     (float32, shaped like the residual) its rows are written, rounded, into columns width .. 2 width - 1 of out."""
     _need(residual, "residual", torch.float32)
     width = residual.shape[1]
     def spec(norm):
         if norm is None:
-            return 0, None, None, 0.0
-        kind, weight, bias, eps = norm
+            return 0, None, None, 0.0, 1, 1.0
+        kind, weight, bias, eps = norm[:4]
+        groups, scale = (norm[4], norm[5]) if len(norm) > 4 else (1, 1.0)
+        if groups < 1 or width % groups or (groups > 1 and kind != "rms"):
+            raise KernelError(f"norm_add_norm: {width} entries in {groups} parts of a {kind} norm are not taken")
         for name, tensor in (("weight", weight), ("bias", bias)):
             if tensor is not None:
                 _need(tensor, name, torch.float32)
                 if tensor.numel() != width:
                     raise KernelError(f"norm_add_norm: a norm's {name} must have {width} entries")
-        return NORM_KINDS[kind], weight, bias, float(eps)
-    inner_kind, inner_w, inner_b, inner_eps = spec(inner)
-    outer_kind, outer_w, outer_b, outer_eps = spec(outer)
+        return NORM_KINDS[kind], weight, bias, float(eps), int(groups), float(scale)
+    inner_kind, inner_w, inner_b, inner_eps, inner_groups, inner_scale = spec(inner)
+    outer_kind, outer_w, outer_b, outer_eps, outer_groups, outer_scale = spec(outer)
     whole = as_float = None
     if delta is not None:
         _need(delta, "delta")
@@ -261,21 +265,28 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
     if row_index is not None:
         _need(row_index, "row_index", torch.int32)
     lib = load_library("elementwise")
-    _check(lib, lib.srb_norm_add_norm(
+    _check(lib, lib.srb_norm_add_norm_ex(
         _ptr(residual), _ptr(whole), _ptr(as_float), inner_kind, _ptr(inner_w), _ptr(inner_b), ctypes.c_float(inner_eps),
-        outer_kind, _ptr(outer_w), _ptr(outer_b), ctypes.c_float(outer_eps), _ptr(out), ctypes.c_longlong(pitch),
+        inner_groups, ctypes.c_float(inner_scale), outer_kind, _ptr(outer_w), _ptr(outer_b), ctypes.c_float(outer_eps),
+        outer_groups, ctypes.c_float(outer_scale), _ptr(out), ctypes.c_longlong(pitch),
         _ptr(extra), _ptr(row_index), rows, width, int(write_residual), dtype_code(dtype), _stream()))
 
 
 #: activations of a gated feed-forward, act(gate) * up, by the numbers of csrc/activations.cuh
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2, "swiglu_clamp": 3}
+#: activations with a parameter (``swiglu_clamp``: min(g, limit) sigmoid(1.702 min(g, limit)) (clamp(u, -limit, limit) + 1),
+#: the parameter being the limit); only the experts' products carry one (``routed_experts(activation_param=)``)
+PARAMETRIC_ACTIVATIONS = frozenset({"swiglu_clamp"})
 
 
-def activation_code(name: str) -> int:
+def activation_code(name: str, parametric: bool = False) -> int:
     try:
-        return ACTIVATIONS[name]
+        code = ACTIVATIONS[name]
     except KeyError:
         raise KernelError(f"unknown activation {name!r}; the kernels have {sorted(ACTIVATIONS)}") from None
+    if name in PARAMETRIC_ACTIVATIONS and not parametric:
+        raise KernelError(f"activation {name!r} has a parameter, which this kernel does not take")
+    return code
 
 
 @traced("activation")
@@ -444,14 +455,17 @@ def latent_attention_takes(dtype: torch.dtype, row_dim: int, value_dim: int) -> 
 def latent_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
                      row_request: torch.Tensor, block_table: torch.Tensor, *, scale: float, sinks: Optional[torch.Tensor],
                      error_word: torch.Tensor, tiles: Optional[torch.Tensor] = None, split_size: int = 0, max_splits: int = 1,
-                     scratch_acc: Optional[torch.Tensor] = None, scratch_ml: Optional[torch.Tensor] = None) -> None:
+                     scratch_acc: Optional[torch.Tensor] = None, scratch_ml: Optional[torch.Tensor] = None,
+                     window: int = 0) -> None:
     """Attention of ``n_q`` query heads over cache rows that are key (the whole row) and value (its first
     ``out.shape[2]`` entries), bfloat16 on the tensor cores, with an optional sink per head.
 
     With ``tiles`` (int32 [n, 4]: first row, rows <= 64, request, first position) the rows of the tiles are prompt
     portions: every row sees the keys up to its own position, and rows outside the tiles are left untouched.  Without,
     every row of ``q`` is one decoded token whose keys are cut every ``split_size`` positions (a multiple of 64); partial
-    results go through the scratch tensors (rows * n_q * max_splits * value_dim and rows * n_q * max_splits * 2 floats)."""
+    results go through the scratch tensors (rows * n_q * max_splits * value_dim and rows * n_q * max_splits * 2 floats).
+    ``window`` > 0: a row sees itself and the ``window`` - 1 keys before it; splits are then counted from the split of a
+    row's first visible key, as the planner of a window group counts them."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(pool, "pool", torch.bfloat16)
     _need(positions, "positions", torch.int32); _need(row_request, "row_request", torch.int32)
     _need(block_table, "block_table", torch.int32)
@@ -476,10 +490,10 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, pos
             raise KernelError("latent_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
     lib = load_library("attention_latent")
-    _check(lib, lib.srb_latent_attention(
+    _check(lib, lib.srb_latent_attention_masked(
         _ptr(q), _ptr(pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions), _ptr(row_request),
         _ptr(block_table), block_table.stride(0), rows, n_q, row_dim, value_dim, page_size, num_pages, int(split_size),
-        int(max_splits), _ptr(tiles), num_tiles, ctypes.c_float(scale), _ptr(sinks), _ptr(error_word), _stream()),
+        int(max_splits), _ptr(tiles), num_tiles, ctypes.c_float(scale), _ptr(sinks), int(window), _ptr(error_word), _stream()),
         launches=1 if tiles is not None else 2)
 
 
@@ -697,18 +711,25 @@ GROUPED_EXPERTS = os.environ.get("SRB_GROUPED_EXPERTS", "1") not in ("0", "off",
 ROUTER_PRODUCT_MIN_ROWS = 128
 #: slots of a tile of the grouped products (128 or 256): 256 reads an expert's weight tile once for twice as many rows
 GROUPED_TILE_SLOTS = int(os.environ.get("SRB_GROUPED_TILE_SLOTS", "256"))
+#: how a router's logits become scores, by the numbers of csrc/moe.cu
+ROUTER_SCORING = {"softmax": 0, "sigmoid": 1}
 
 
 @traced("routed_experts")
 def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
                    activation: str, renormalize: bool, error_word: torch.Tensor, *, gated: bool = True,
-                   router_bias: Optional[torch.Tensor] = None, base: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   router_bias: Optional[torch.Tensor] = None, base: Optional[torch.Tensor] = None,
+                   scoring: str = "softmax", choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0,
+                   norm_eps: float = 0.0, activation_param: float = 0.0) -> torch.Tensor:
     """sum over the ``top`` experts with the largest router scores of score * expert(h), float32 [rows, width].
 
     ``gated`` False: an expert is W_down act(W_up h) and ``w_gate_up`` holds the up matrices alone
     [experts, inner, width].  ``router_bias`` (float32 [experts]) is added to the router's logits before the choice.
     ``base`` (float32 [rows, width]): a term that every row gets beside its experts' (an expert that all rows
-    share); the sum starts from it.
+    share); the sum starts from it.  ``scoring`` ``sigmoid``: an expert's score is the sigmoid of its logit instead of
+    the softmax over all; ``choice_bias`` (float32 [experts]) is added to the scores for the choice only; the weights
+    are the chosen scores, with ``renormalize`` divided by (their sum + ``norm_eps``), then times ``weight_scale``.
+    ``activation_param``: the parameter of an activation that has one.
 
     ``router`` [experts, width]; ``w_gate_up`` [experts, 2 * inner, width] (an expert's gate rows over its up rows);
     ``w_down`` [experts, width, inner], all of h's dtype.  Scores are a softmax over all experts, in 32-bit; with
@@ -733,6 +754,12 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
         _need(base, "base", torch.float32)
         if base.shape != (rows, width):
             raise KernelError("routed_experts: the shared term must be float32 [rows, width]")
+    if choice_bias is not None:
+        _need(choice_bias, "choice_bias", torch.float32)
+        if choice_bias.numel() != experts:
+            raise KernelError("routed_experts: one choice bias per expert is needed")
+    rule = (int(renormalize), ROUTER_SCORING[scoring], _ptr(choice_bias), ctypes.c_float(weight_scale), ctypes.c_float(norm_eps))
+    act_code, act_param = activation_code(activation, parametric=True), ctypes.c_float(activation_param)
     lib = load_library("moe")
     device = h.device
     entries = rows * top
@@ -751,11 +778,11 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     if rows >= ROUTER_PRODUCT_MIN_ROWS or router_bias is not None:
         # many rows: the logits are a product like any other (32-bit accumulation, 32-bit result), the choice a kernel of its own
         logits = linear(h, router, router_bias, out_dtype=torch.float32, error_word=error_word)
-        _check(lib, lib.srb_moe_select(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, experts, top, int(renormalize),
-                                       _ptr(chosen), _ptr(weights), stream))
+        _check(lib, lib.srb_moe_select_ex(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, experts, top, *rule,
+                                          _ptr(chosen), _ptr(weights), stream))
     else:
-        _check(lib, lib.srb_moe_route(_ptr(h), _ptr(router), rows, width, experts, top, int(renormalize), _ptr(chosen),
-                                      _ptr(weights), code, stream))
+        _check(lib, lib.srb_moe_route_ex(_ptr(h), _ptr(router), rows, width, experts, top, *rule, _ptr(chosen),
+                                         _ptr(weights), code, stream))
     _check(lib, lib.srb_moe_plan_of(_ptr(chosen), rows, top, experts, tile_slots, _ptr(plan), _ptr(slot_row),
                                     _ptr(entry_slot), _ptr(error_word), stream))
     if grouped:
@@ -766,20 +793,20 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
         _check(product, product.srb_gemm_bf16_grouped(
             _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, tile_slots, entries, experts,
             (2 if gated else 1) * inner, inner, width, inner, inner if gated else 0, GEMM_MODES["gated" if gated else "act"],
-            activation_code(activation), _ptr(error_word), stream))
+            act_code, act_param, _ptr(error_word), stream))
         _check(product, product.srb_gemm_bf16_grouped(
             _ptr(act), _ptr(w_down), _ptr(y), _ptr(plan), max_tiles, tile_slots, entries, experts, width, width, inner, width, 0,
-            GEMM_MODES["f32"], 0, _ptr(error_word), stream))
+            GEMM_MODES["f32"], 0, ctypes.c_float(0.0), _ptr(error_word), stream))
     else:
         element = h.element_size()
         if gated:
             w_up = ctypes.c_void_p(w_gate_up.data_ptr() + inner * width * element)
             _check(lib, lib.srb_moe_gated_up(_ptr(h), _ptr(w_gate_up), w_up, ctypes.c_longlong(2 * inner * width), _ptr(plan),
-                                             _ptr(slot_row), rows, top, experts, width, inner, activation_code(activation),
+                                             _ptr(slot_row), rows, top, experts, width, inner, act_code, act_param,
                                              _ptr(act), code, stream))
         else:
             _check(lib, lib.srb_moe_act_up(_ptr(h), _ptr(w_gate_up), _ptr(plan), _ptr(slot_row), rows, top, experts, width,
-                                           inner, activation_code(activation), _ptr(act), code, stream))
+                                           inner, act_code, act_param, _ptr(act), code, stream))
         _check(lib, lib.srb_moe_down(_ptr(act), _ptr(w_down), _ptr(plan), rows, top, experts, width, inner, _ptr(y), code,
                                      stream))
     _check(lib, lib.srb_moe_combine_onto(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), _ptr(base),
@@ -787,15 +814,20 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     return out
 
 
-def route(h: torch.Tensor, router: torch.Tensor, top: int, renormalize: bool = False):
-    """The router alone: (chosen experts int32 [rows, top], their weights float32 [rows, top])."""
+def route(h: torch.Tensor, router: torch.Tensor, top: int, renormalize: bool = False, *, scoring: str = "softmax",
+          choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0, norm_eps: float = 0.0):
+    """The router alone: (chosen experts int32 [rows, top], their weights float32 [rows, top]); the options are
+    those of :func:`routed_experts`."""
     _need(h, "h"); _need(router, "router", h.dtype)
+    if choice_bias is not None:
+        _need(choice_bias, "choice_bias", torch.float32)
     rows, width = h.shape
     chosen = torch.empty((rows, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((rows, top), dtype=torch.float32, device=h.device)
     lib = load_library("moe")
-    _check(lib, lib.srb_moe_route(_ptr(h), _ptr(router), rows, width, router.shape[0], top, int(renormalize), _ptr(chosen),
-                                  _ptr(weights), dtype_code(h.dtype), _stream()))
+    _check(lib, lib.srb_moe_route_ex(_ptr(h), _ptr(router), rows, width, router.shape[0], top, int(renormalize),
+                                     ROUTER_SCORING[scoring], _ptr(choice_bias), ctypes.c_float(weight_scale),
+                                     ctypes.c_float(norm_eps), _ptr(chosen), _ptr(weights), dtype_code(h.dtype), _stream()))
     return chosen, weights
 
 
@@ -1202,6 +1234,146 @@ def lightning_gate_norm(o: torch.Tensor, proj: torch.Tensor, g_offset: int, weig
 
 
 # --------------------------------------------------------------------------- sampling
+
+# --------------------------------------------------------------------------- a state-space mixer over a state per request
+
+def mamba_slot_floats(heads: int, vdim: int, nstate: int, groups: int, taps: int) -> int:
+    """Floats of state per request: the convolution's last ``taps`` - 1 inputs [taps - 1, channels], then S [heads, vdim, nstate]."""
+    return (taps - 1) * (heads * vdim + 2 * groups * nstate) + heads * nstate * vdim
+
+
+def _mamba_args(proj, state, heads, vdim, nstate, groups, taps):
+    if proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("mamba: the in-projection must be a CUDA matrix with dense rows")
+    _need(state, "state", torch.float32)
+    if state.dim() != 2 or state.shape[1] != mamba_slot_floats(heads, vdim, nstate, groups, taps):
+        raise KernelError("mamba: the state must be float32 [slots, floats per slot]")
+    if proj.shape[1] < 2 * heads * vdim + 2 * groups * nstate + heads:
+        raise KernelError("mamba: rows of the in-projection are too short")
+
+
+@traced("mamba_conv")
+def mamba_conv(proj: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, positions: torch.Tensor, row_request: torch.Tensor,
+               cu_rows: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, num_requests: int, *,
+               heads: int, vdim: int, nstate: int, groups: int, taps: int, read_only: bool = False) -> None:
+    """The causal convolution per channel and SiLU of the x, B and C entries of ``proj``'s rows
+    ([z | x | B | C | dt]); ``out`` float32 [rows, channels].  Inputs before a request's first row of the step come from
+    its slot of ``state`` (zeros before position 0); unless ``read_only`` the slot then keeps the sequence's last
+    ``taps`` - 1 inputs.  ``weight`` float32 [channels, taps] (the last column is the current token's), ``bias`` [channels]."""
+    _mamba_args(proj, state, heads, vdim, nstate, groups, taps)
+    channels = heads * vdim + 2 * groups * nstate
+    _need(weight, "weight", torch.float32); _need(bias, "bias", torch.float32); _need(out, "out", torch.float32)
+    for name, t in (("positions", positions), ("row_request", row_request), ("cu_rows", cu_rows), ("state_slots", state_slots)):
+        _need(t, name, torch.int32)
+    rows = proj.shape[0]
+    if weight.shape != (channels, taps) or bias.numel() != channels or out.shape != (rows, channels):
+        raise KernelError("mamba_conv: shapes of the filter, its bias and the output do not agree")
+    lib = load_library("mamba")
+    _check(lib, lib.srb_mamba_conv(_ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(weight), _ptr(bias), _ptr(positions),
+                                   _ptr(row_request), _ptr(cu_rows), _ptr(state_slots), _ptr(state),
+                                   ctypes.c_longlong(state.stride(0)), _ptr(out), rows, int(num_requests), heads, vdim, nstate,
+                                   groups, taps, int(not read_only), dtype_code(proj.dtype), _stream()),
+           launches=1 if read_only or taps == 1 else 2)
+
+
+@traced("mamba_scan")
+def mamba_scan(proj: torch.Tensor, xbc: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, dt_bias: torch.Tensor,
+               positions: torch.Tensor, cu_rows: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor,
+               num_requests: int, *, heads: int, vdim: int, nstate: int, groups: int, taps: int, read_only: bool = False) -> None:
+    """The recurrence per head, token by token from each request's state: dt = softplus(dt + dt_bias), S <- exp(-exp(A_log) dt) S
+    + dt B x^T, y = S^T C + D x, all in 32-bit.  ``xbc``: what :func:`mamba_conv` wrote; ``y`` float32 [rows, heads * vdim]."""
+    _mamba_args(proj, state, heads, vdim, nstate, groups, taps)
+    rows, inner = proj.shape[0], heads * vdim
+    _need(xbc, "xbc", torch.float32); _need(y, "y", torch.float32)
+    for name, t in (("a_log", a_log), ("d_skip", d_skip), ("dt_bias", dt_bias)):
+        _need(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"mamba_scan: {name} needs one entry per head")
+    for name, t in (("positions", positions), ("cu_rows", cu_rows), ("state_slots", state_slots)):
+        _need(t, name, torch.int32)
+    if xbc.shape != (rows, inner + 2 * groups * nstate) or y.shape != (rows, inner):
+        raise KernelError("mamba_scan: shapes of the convolved inputs and the output do not agree")
+    lib = load_library("mamba")
+    _check(lib, lib.srb_mamba_scan(_ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(xbc), _ptr(a_log), _ptr(d_skip),
+                                   _ptr(dt_bias), _ptr(positions), _ptr(cu_rows), _ptr(state_slots), _ptr(state),
+                                   ctypes.c_longlong(state.stride(0)), _ptr(y), rows, int(num_requests), heads, vdim, nstate, groups,
+                                   taps, int(not read_only), dtype_code(proj.dtype), _stream()))
+
+
+@traced("mamba_gate_norm")
+def mamba_gate_norm(y: torch.Tensor, proj: torch.Tensor, weight: torch.Tensor, eps: float, norm_groups: int,
+                    out: torch.Tensor) -> None:
+    """out = rms_in_parts(y * silu(z)) * weight with z the first entries of ``proj``'s rows and the RMS norm taken in
+    ``norm_groups`` equal consecutive parts; y float32 [rows, inner], out [rows, inner] of proj's dtype."""
+    _need(y, "y", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out", proj.dtype)
+    rows, inner = y.shape
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[0] != rows or proj.shape[1] < inner or weight.numel() != inner \
+            or out.shape != (rows, inner):
+        raise KernelError("mamba_gate_norm: shapes do not agree")
+    lib = load_library("mamba")
+    _check(lib, lib.srb_mamba_gate_norm(_ptr(y), _ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(weight), ctypes.c_float(eps),
+                                        rows, inner, int(norm_groups), _ptr(out), dtype_code(proj.dtype), _stream()))
+
+
+# --------------------------------------------------------------------------- sublayers side by side, a token's own input
+
+@traced("residual")
+def scaled_sum(residual: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], mult: float,
+               rounded: Optional[torch.Tensor] = None) -> None:
+    """residual += mult * (a + b) in 32-bit, in place.  ``a``: [rows, width] of the compute dtype or float32, or float32
+    [parts, rows, width] (partial sums, added in order), or None; ``b``: float32 [rows, width] or None.  ``rounded``
+    ([rows, width]) receives the new residual rounded to its dtype."""
+    _need(residual, "residual", torch.float32)
+    rows, width = residual.shape
+    whole = parts = None
+    num_parts = stride = 0
+    dtype = rounded.dtype if rounded is not None else (a.dtype if a is not None else torch.float32)
+    if a is not None:
+        _need(a, "a")
+        if a.dtype == torch.float32:
+            parts = a if a.dim() == 3 else a.unsqueeze(0)
+            if parts.shape[1:] != residual.shape:
+                raise KernelError("scaled_sum: a and the residual differ in shape")
+            num_parts, stride = parts.shape[0], parts.stride(0)
+        else:
+            if a.shape != residual.shape or a.dtype != dtype:
+                raise KernelError("scaled_sum: a must be shaped like the residual, of the rounded copy's dtype")
+            whole = a
+    if b is not None:
+        _need(b, "b", torch.float32)
+        if b.shape != residual.shape:
+            raise KernelError("scaled_sum: b and the residual differ in shape")
+    if rounded is not None:
+        _need(rounded, "rounded")
+        if rounded.shape != residual.shape:
+            raise KernelError("scaled_sum: the rounded copy and the residual differ in shape")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_scaled_sum(_ptr(residual), _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(stride), _ptr(b),
+                                   ctypes.c_float(mult), _ptr(rounded), rows, width, dtype_code(dtype), _stream()))
+
+
+@traced("activation")
+def token_gate(gate: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, offset: int, out: torch.Tensor, error_word: torch.Tensor,
+               activation: str = "gelu_tanh") -> None:
+    """out[r, j] = act(gate[r, j]) * table[ids[r], offset + j]: a gate multiplied by a slice of the row that the token
+    chooses in ``table`` [vocab, >= offset + dim]."""
+    _need(gate, "gate"); _need(out, "out", gate.dtype); _need(table, "table", gate.dtype); _need(ids, "ids", torch.int32)
+    rows, dim = gate.shape
+    if out.shape != gate.shape or ids.numel() != rows or table.dim() != 2 or offset < 0 or offset + dim > table.shape[1]:
+        raise KernelError("token_gate: shapes do not agree")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_token_gate(_ptr(gate), _ptr(ids), _ptr(table), ctypes.c_longlong(table.stride(0)), int(offset),
+                                   table.shape[0], rows, dim, activation_code(activation), _ptr(out), _ptr(error_word),
+                                   dtype_code(gate.dtype), _stream()))
+
+
+@traced("logits")
+def scale_values(values: torch.Tensor, factor: float) -> None:
+    """values *= factor, float32, in place."""
+    _need(values, "values", torch.float32)
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_scale_values(_ptr(values), ctypes.c_longlong(values.numel()), ctypes.c_float(factor), _stream()))
+
 
 @traced("sampling")
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],

@@ -1,7 +1,7 @@
 from .attention import AttentionNames, GroupedQueryAttention
 from .base import (CacheNeed, FeedForward, Mixer, Norm, NormedDelta, PagedKV, Part, PositionEncoding, RequestState,
                    TensorSpec, matrix_to, scale_to)
-from .block import PreNormBlock, SandwichBlock
+from .block import ParallelBlock, PreNormBlock, SandwichBlock
 from .latent_attention import LatentAttention, LatentAttentionNames
 from .loop import PassEntry
 from .moe import RoutedExperts
@@ -9,7 +9,9 @@ from .embedding import OutputHead, PairTokenEmbedding, TokenEmbedding
 from .hyper import StreamBlock, StreamConnection, StreamNames, StreamSumNorm, StreamUpdate
 from .lightning import LightningAttention, LightningNames
 from .mlp import GatedMlp, GatedMlpNames, PlainMlp
-from .norm import LayerNorm, RmsNorm
+from .mamba import MambaMixer, MambaNames
+from .norm import GroupedRmsNorm, LayerNorm, RmsNorm
+from .side import TokenSideInput, TokenSideNames
 from .rope import NoPositionEncoding, RotaryEncoding, WavelengthScaling
 
 __all__ = [
@@ -19,4 +21,5 @@ __all__ = [
     "SandwichBlock", "LatentAttention", "LatentAttentionNames", "PassEntry", "RoutedExperts", "LayerNorm",
     "PairTokenEmbedding", "StreamBlock", "StreamConnection", "StreamNames", "StreamSumNorm", "StreamUpdate",
     "LightningAttention", "LightningNames", "PlainMlp", "WavelengthScaling",
+    "ParallelBlock", "GroupedRmsNorm", "MambaMixer", "MambaNames", "TokenSideInput", "TokenSideNames",
 ]

@@ -3,7 +3,8 @@
 Pre-norm residual form (reference: crates/sglang-srt/src/cpu_reference.rs:257-317):
 h' = h + mixer(norm_1(h)); h'' = h' + feed_forward(norm_2(h')).  The hidden state travels
 as (residual, delta) with h = residual + delta; each norm takes the pending sum first, in
-32-bit, so no separate add kernel runs.
+32-bit, so no separate add kernel runs.  :class:`SandwichBlock` norms each sublayer on both sides;
+:class:`ParallelBlock` runs mixer and feed-forward side by side from one norm.
 """
 from __future__ import annotations
 
@@ -11,6 +12,7 @@ from typing import Dict, Mapping, Optional, Tuple
 
 import torch
 
+from .. import ops
 from .base import FeedForward, Mixer, Norm, NormedDelta, Part, TensorSpec
 
 
@@ -106,3 +108,51 @@ class SandwichBlock(Part):
             return residual, delta
         normed = self.norm_2.add_norm(residual, delta, ctx.dtype)
         return residual, NormedDelta(self.feed_forward.forward(ctx, normed), self.norm_2b)
+
+
+class ParallelBlock(Part):
+    """Both sublayers read ONE norm of the stream and their results are added together:
+    h = norm(x); x <- x + mult * (mixer(h) + feed_forward(h)); without a feed-forward only the mixer's term.  Then,
+    with ``side`` (``parts/side.py``), x <- x + norm_side(side(x)), the side norm carrying its own factor.
+
+    The sum is one kernel (``ops.scaled_sum``: 32-bit, the mixer's result rounded, 32-bit or in partial sums along K, the
+    feed-forward's 32-bit) that also writes the rounded stream the side part's product reads.  The side's result travels
+    on as a :class:`NormedDelta`, so its norm, the residual sum and the next block's norm (or the final norm) are one
+    kernel."""
+
+    def __init__(self, norm: Norm, mixer: Mixer, feed_forward: Optional[FeedForward], mult: float = 1.0, side=None):
+        self.norm, self.mixer, self.feed_forward, self.mult, self.side = norm, mixer, feed_forward, float(mult), side
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part in self.parts())
+
+    def parts(self):
+        return tuple(part for part in (self.norm, self.mixer, self.feed_forward, self.side) if part is not None)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def split_scratch(self):
+        return self.mixer.split_scratch()
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs: Dict[str, TensorSpec] = {}
+        for part in self.parts():
+            specs.update(part.tensor_specs())
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        for part in self.parts():
+            part.load(tensors, device, dtype)
+
+    def forward(self, ctx, cache, residual: torch.Tensor, delta):
+        normed = self.norm.add_norm(residual, delta, ctx.dtype)
+        mixed = self.mixer.forward(ctx, cache, normed)
+        fed = self.feed_forward.forward(ctx, normed) if self.feed_forward is not None else None
+        if self.side is None:
+            ops.scaled_sum(residual, mixed, fed, self.mult)
+            return residual, None
+        rounded = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+        ops.scaled_sum(residual, mixed, fed, self.mult, rounded)
+        return residual, NormedDelta(self.side.forward(ctx, rounded), self.side.norm)

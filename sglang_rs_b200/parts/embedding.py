@@ -21,15 +21,24 @@ from .base import Part, RequestState, TensorSpec, matrix_to
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab: int, width: int, weight_name: str, scale: float = 1.0):
+    def __init__(self, vocab: int, width: int, weight_name: str, scale: float = 1.0,
+                 side_tables: Optional[Mapping[str, int]] = None):
+        """``side_tables``: further tables indexed by the token (checkpoint name -> row width) that other parts read
+        (``parts/side.py``); they are loaded once, here, and found in ``self.side[name]``."""
         self.vocab, self.width, self.weight_name, self.scale = int(vocab), int(width), weight_name, float(scale)
         self.table: Optional[torch.Tensor] = None
+        self.side_tables = dict(side_tables or {})
+        self.side: Dict[str, torch.Tensor] = {}
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.weight_name: TensorSpec((self.vocab, self.width))}
+        specs = {self.weight_name: TensorSpec((self.vocab, self.width))}
+        for name, width in self.side_tables.items():
+            specs[name] = TensorSpec((self.vocab, width))
+        return specs
 
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.table = matrix_to(tensors[self.weight_name], device, dtype)
+        self.side = {name: matrix_to(tensors[name], device, dtype) for name in self.side_tables}
 
     def native_record(self):
         """The step executor reads the table itself; the record says only that there is one (it knows no scale)."""
@@ -95,13 +104,14 @@ class OutputHead(Part):
 
 
     def __init__(self, vocab: int, width: int, weight_name: Optional[str], embedding: Optional[TokenEmbedding] = None,
-                 softcap: Optional[float] = None):
+                 softcap: Optional[float] = None, scale: float = 1.0):
+        """``scale`` multiplies the 32-bit logits (1: as they are)."""
         if weight_name is None and embedding is None:
             raise ValueError("a tied head needs the embedding it shares")
         if softcap is not None and not softcap > 0:
             raise ValueError("the cap of the logits must be positive")
         self.vocab, self.width, self.weight_name, self.embedding = int(vocab), int(width), weight_name, embedding
-        self.softcap = softcap
+        self.softcap, self.scale = softcap, float(scale)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -113,11 +123,13 @@ class OutputHead(Part):
 
     def native_record(self):
         weight = self.weight if self.weight_name else self.embedding.table
-        return None if weight is None or self.softcap is not None else True
+        return None if weight is None or self.softcap is not None or self.scale != 1.0 else True
 
     def forward(self, ctx, normed: torch.Tensor) -> torch.Tensor:
         weight = self.weight if self.weight_name else self.embedding.table
         logits = ops.linear(normed, weight, out_dtype=torch.float32, error_word=ctx.error_word)
+        if self.scale != 1.0:
+            ops.scale_values(logits, self.scale)
         if self.softcap is not None:
             ops.softcap(logits, self.softcap)
         return logits

@@ -12,6 +12,11 @@ Variations, all off by default: experts without a gate, W_down act(W_up h) (``ex
 ``GatedMlpNames`` with ``gate`` None); a bias on the router's logits (``router_bias_name``), added before the
 choice; an expert that every row shares (``shared``: a feed-forward whose 32-bit result is the first term of
 the sum).  A softmax over the chosen logits only is the same as ``renormalize`` over the softmax of all.
+Scores may be the sigmoid of each logit instead of the softmax over all (``scoring="sigmoid"``); a correction per expert
+(``choice_bias_name``) may be added to the scores for the choice alone, the weights using the scores without it; with
+``renormalize`` the chosen scores are divided by their sum plus ``norm_eps``; ``weight_scale`` multiplies the weights.
+An activation with a parameter (``swiglu_clamp``: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit) and
+u' = clamp(u, -limit, limit)) takes it as ``activation_param``.
 """
 from __future__ import annotations
 
@@ -29,9 +34,13 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, hidden: int, inner: int, experts: int, top: int, activation: str, router_name: str,
                  expert_names: Callable[[int], GatedMlpNames], renormalize: bool = False, *,
-                 router_bias_name: Optional[str] = None, shared: Optional[FeedForward] = None):
+                 router_bias_name: Optional[str] = None, shared: Optional[FeedForward] = None,
+                 scoring: str = "softmax", choice_bias_name: Optional[str] = None, weight_scale: float = 1.0,
+                 norm_eps: float = 0.0, activation_param: float = 0.0):
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"unsupported activation {activation}; available: {sorted(ops.ACTIVATIONS)}")
+        if scoring not in ops.ROUTER_SCORING:
+            raise ValueError(f"unsupported scoring {scoring}; available: {sorted(ops.ROUTER_SCORING)}")
         if not 0 < top <= experts:
             raise ValueError(f"{top} chosen experts of {experts}")
         if experts > 1024 or top > 32:
@@ -43,12 +52,16 @@ class RoutedExperts(FeedForward):
         if any((n.gate is not None) != self.gated for n in self.names):
             raise ValueError("the experts of one layer have a gate or have none, all alike")
         self.router_bias_name, self.shared = router_bias_name, shared
-        self.router = self.w_gate_up = self.w_down = self.router_bias = None
+        self.scoring, self.choice_bias_name = scoring, choice_bias_name
+        self.weight_scale, self.norm_eps, self.activation_param = float(weight_scale), float(norm_eps), float(activation_param)
+        self.router = self.w_gate_up = self.w_down = self.router_bias = self.choice_bias = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {self.router_name: TensorSpec((self.experts, self.hidden))}
         if self.router_bias_name:
             specs[self.router_bias_name] = TensorSpec((self.experts,))
+        if self.choice_bias_name:
+            specs[self.choice_bias_name] = TensorSpec((self.experts,))
         if self.shared is not None:
             specs.update(self.shared.tensor_specs())
         for n in self.names:
@@ -67,6 +80,7 @@ class RoutedExperts(FeedForward):
             stacked = [tensors[n.up] for n in self.names]
         self.w_gate_up = matrix_to(torch.stack(stacked), device, dtype)
         self.router_bias = scale_to(tensors[self.router_bias_name], device) if self.router_bias_name else None
+        self.choice_bias = scale_to(tensors[self.choice_bias_name], device) if self.choice_bias_name else None
         if self.shared is not None:
             self.shared.load(tensors, device, dtype)
         self.w_down = matrix_to(torch.stack([tensors[n.down] for n in self.names]), device, dtype)
@@ -77,4 +91,6 @@ class RoutedExperts(FeedForward):
             raise TypeError("the shared expert must give a 32-bit result [rows, width]")
         return ops.routed_experts(x, self.router, self.w_gate_up, self.w_down, self.top, self.activation,
                                   self.renormalize, ctx.error_word, gated=self.gated, router_bias=self.router_bias,
-                                  base=base)
+                                  base=base, scoring=self.scoring, choice_bias=self.choice_bias,
+                                  weight_scale=self.weight_scale, norm_eps=self.norm_eps,
+                                  activation_param=self.activation_param)

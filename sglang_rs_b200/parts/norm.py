@@ -47,6 +47,38 @@ class RmsNorm(Norm):
         return out
 
 
+class GroupedRmsNorm(Norm):
+    """An RMS norm taken in ``groups`` equal consecutive parts of the row: each part is divided by its own
+    sqrt(mean(part^2) + eps), then the whole row is multiplied by the weight and by ``scale`` (a constant, 1 unless a
+    design weighs the normed term in a residual sum).  With one group and scale 1 it is the plain RMS norm.  Like
+    :class:`LayerNorm` it takes the pending term as a tensor or as a :class:`NormedDelta`, so a norm behind a sublayer,
+    the residual sum and this norm run in one kernel; means, roots and the sum are 32-bit."""
+    graph_safe = True
+
+    def __init__(self, width: int, eps: float, weight_name: str, groups: int = 1, scale: float = 1.0):
+        if groups < 1 or width % groups:
+            raise ValueError(f"a row of {width} entries does not split into {groups} equal parts")
+        self.width, self.eps, self.weight_name = int(width), float(eps), weight_name
+        self.groups, self.scale = int(groups), float(scale)
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.weight_name: TensorSpec((self.width,), "scale")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        self.weight = scale_to(tensors[self.weight_name], device)
+
+    def spec(self):
+        return ("rms", self.weight, None, self.eps, self.groups, self.scale)
+
+    def add_norm(self, residual: torch.Tensor, delta, out_dtype: torch.dtype,
+                 row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+        rows = residual.shape[0] if row_index is None else row_index.numel()
+        out = torch.empty((rows, self.width), dtype=out_dtype, device=residual.device)
+        add_pending(residual, delta, self.spec(), out, row_index)
+        return out
+
+
 class LayerNorm(Norm):
     """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b, eps inside the root, all in 32-bit.
 
