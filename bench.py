@@ -159,7 +159,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel", "tosivik"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel", "tosivik", "desarax"))
     parser.add_argument("--rows", default="1,8,64,2048", help="--mode compare-cublas: the row counts, comma-separated")
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
@@ -172,7 +172,7 @@ def main() -> int:
     parser.add_argument("--requests", type=int, default=128, help="--mode serve: number of requests")
     parser.add_argument("--seed", type=int, default=0)
     parser.add_argument("--width", type=int, default=2048, choices=(1024, 2048, 4096),
-                        help="--mode tosivik: the model's width; heads, feed-forwards and the Qwen3 shape beside it follow")
+                        help="--mode tosivik and --mode desarax: the model's width; heads, feed-forwards and the shape beside it follow")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -189,6 +189,8 @@ def main() -> int:
         return gegepel_beside_qwen3(args, warmup)
     if args.mode == "tosivik":
         return tosivik_beside_qwen3(args, warmup)
+    if args.mode == "desarax":
+        return desarax_beside_tosivik(args, warmup)
 
     if args.mode == "timeline":
         # the kernels of a decode step, built with marks that record when each block starts, stops waiting for the
@@ -864,6 +866,45 @@ def tosivik_beside_qwen3(args, warmup) -> int:
     note = {"layers": layers, "width": args.width, "vocab": vocab, "tosivik_layers": designs["tosivik"]["layers"][:4],
             "streams": 4, "qwen3_shape": beside}
     return designs_side_by_side(args, warmup, "tosivik", designs, vocab, note)
+
+
+def desarax_layers(width: int, count: int):
+    """Layers of a real model's size at ``width``: state-space mixers with heads of 64 columns over states of 128 entries
+    (inner = twice the width, eight groups of B and C, a convolution over four tokens, the gated norm in eight parts);
+    attention through latents of 512 entries with heads of 128 and a window of 1,024 positions, every second attention
+    layer reading the latents of the one before; 64 clamped experts of 11/16 of the width (6 chosen) in every layer.
+    The kinds alternate as state-space, state-space, attention, attention on the first one's latents."""
+    heads = width // 128
+    state_space = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+    attention = {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 1.0 / math.sqrt(128), "mask": {"size": 1024}}
+    experts = {"kind": "moe", "router": {"experts": 64, "top": 6, "scale": 2.5}, "expert": {"ff": 11 * width // 16, "limit": 7.0}}
+    layers = []
+    for i in range(count):
+        if i % 4 < 2:
+            layers.append({"type": "mamba2" if i % 4 == 0 else "mamba2_2", "mixer": state_space, "mlp": experts})
+        elif i % 4 == 2:
+            layers.append({"type": "latent_attention", "mixer": attention, "mlp": experts})
+        else:
+            layers.append({"type": "latent_attention", "mixer": dict(attention, kv_from=i - 1), "mlp": experts})
+    return layers
+
+
+def desarax_beside_tosivik(args, warmup) -> int:
+    """``--mode desarax``: prefill and decode of a Desarax model with layers of a real model's size (random weights)
+    beside a Tosivik model of equal width and depth (the closest design: a recurrent mixer over a state per request and
+    routed experts), as ``--mode tosivik`` does for that design.  ``--width`` 1024, 2048 or 4096."""
+    layers = args.layers if args.layers is not None else 4
+    vocab = 32768
+    designs = {
+        "desarax": {"architecture": "Desarax", "vocab": vocab, "width": args.width, "residual_mult": 0.5, "logit_scale": 0.25,
+                    "norm": {"eps": 1e-5, "groups": 4}, "token_side": {"dim": 256}, "layers": desarax_layers(args.width, layers)},
+        "tosivik": {"architecture": "Tosivik", "vocab": vocab, "width": args.width, "streams": 4, "logit_softcap": 30.0,
+                    "embedding": {"scale": math.sqrt(args.width), "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+                    "norm": {"eps": 1e-5}, "layers": tosivik_layers(args.width, layers)},
+    }
+    note = {"layers": layers, "width": args.width, "vocab": vocab, "desarax_layers": designs["desarax"]["layers"][:4],
+            "tosivik_layers": designs["tosivik"]["layers"][:4]}
+    return designs_side_by_side(args, warmup, "desarax", designs, vocab, note)
 
 
 def designs_side_by_side(args, warmup, mode, designs, vocab, note) -> int:
