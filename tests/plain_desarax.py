@@ -54,6 +54,24 @@ def causal_conv(u, weight, bias):
     return out
 
 
+def recurrence(x, B, C, dt, a_log, skip, begin=None):
+    """x [T, heads, P], B and C [T, G, N], dt [T, heads] (after the softplus): per head S <- exp(-exp(a_log) dt) S + dt B x^T,
+    y = S^T C + skip x, from the states ``begin`` [heads, N, P] (zeros without).  Returns (y [T, heads, P], the last states)."""
+    T, heads, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    y = torch.zeros(T, heads, P, dtype=F)
+    last = torch.zeros(heads, N, P, dtype=F)
+    for head in range(heads):
+        g = head // (heads // G)
+        S = torch.zeros(N, P, dtype=F) if begin is None else begin[head].clone()
+        rate = torch.exp(a_log[head])
+        for t in range(T):
+            S = torch.exp(-rate * dt[t, head]) * S + dt[t, head] * torch.outer(B[t, g], x[t, head])
+            y[t, head] = S.T @ C[t, g] + skip[head] * x[t, head]
+        last[head] = S
+    return y, last
+
+
 def mamba2(h, w, m, eps):
     """The state-space mixer over a whole sequence h [T, width]; ``w`` maps the short names (in, conv, conv.b, dt_bias,
     A_log, D, norm, o) to tensors; ``m`` is the mixer's section of the document."""
@@ -66,15 +84,7 @@ def mamba2(h, w, m, eps):
     x = xbc[:, :inner].reshape(T, heads, P)
     B = xbc[:, inner:inner + G * N].reshape(T, G, N)
     C = xbc[:, inner + G * N:].reshape(T, G, N)
-    dt = softplus(dt + w["dt_bias"])
-    y = torch.zeros(T, heads, P, dtype=F)
-    for head in range(heads):
-        g = head // (heads // G)
-        S = torch.zeros(N, P, dtype=F)
-        a = -torch.exp(w["A_log"][head])
-        for t in range(T):
-            S = torch.exp(a * dt[t, head]) * S + dt[t, head] * torch.outer(B[t, g], x[t, head])
-            y[t, head] = S.T @ C[t, g] + w["D"][head] * x[t, head]
+    y, _ = recurrence(x, B, C, softplus(dt + w["dt_bias"]), w["A_log"], w["D"])
     y = y.reshape(T, inner) * silu(z)
     y = group_norm(y, w["norm"], m["norm_groups"], eps)
     return y @ w["o"].T
@@ -120,7 +130,7 @@ def route(h, router, correction, top, scale):
 
 def routed_experts(h, w, f):
     """``w``: short names (router, correction, e<j>.gate / up / down); ``f``: the feed-forward's section."""
-    top, scale, limit = f["router"]["top"], f["router"]["scale"], f["expert"]["limit"]
+    top, scale, limit = f["router"]["top"], f["router"].get("scale", 1.0), f["expert"]["limit"]
     chosen, weights = route(h, w["router"], w["correction"], top, scale)
     out = torch.zeros(h.shape[0], w["e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
@@ -144,7 +154,7 @@ def short_names(tensors, prefix):
 def forward(config, tensors, tokens, return_layers=False):
     """Logits [T, vocab] of a whole sequence; with ``return_layers`` also the stream after every layer."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    eps, groups, mult = config["norm"]["eps"], config["norm"]["groups"], config["residual_mult"]
+    eps, groups, mult = config["norm"]["eps"], config["norm"].get("groups", 1), config.get("residual_mult", 1.0)
     embed = tensors["embed"].to(F)
     x = embed[tokens]
     latents, after = {}, []
@@ -167,5 +177,5 @@ def forward(config, tensors, tokens, return_layers=False):
             x = token_side(x, tokens, tensors["side.embed"].to(F), i, config["token_side"]["dim"],
                            short_names(tensors, p + "side."), eps, mult)
         after.append(x)
-    logits = group_norm(x, tensors["final.norm"].to(F), groups, eps) @ embed.T * config["logit_scale"]
+    logits = group_norm(x, tensors["final.norm"].to(F), groups, eps) @ embed.T * config.get("logit_scale", 1.0)
     return (logits, torch.stack(after)) if return_layers else logits
