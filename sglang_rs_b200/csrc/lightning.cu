@@ -294,11 +294,9 @@ extern "C" int srb_lightning_gate_norm(const float* o, const void* proj, long lo
 // state) goes in as the sum of two bfloat16 numbers, its rounding and the rounding of the rest, in two products: 16
 // bits of mantissa survive.  Operands lie in shared memory with the contraction index contiguous and rows padded by
 // 16 bytes, so a fragment is four (or two) conflict-free 32-bit loads.
-#include "mma_helpers.cuh"
-#define LC_TOKENS 128
+#include "chunk_helpers.cuh"
 #define LC_THREADS 128
 #define LC_OUT_THREADS (LC_TOKENS * 2)      // the results kernel: a warp per sixteen rows of the chunk
-#define LC_PAD 8
 
 struct LightningChunkArgs {
   const __nv_bfloat16* proj;
@@ -340,22 +338,6 @@ __device__ __forceinline__ void lc_powers(float* power, float decay) {     // po
   }
 }
 
-__device__ __forceinline__ unsigned lc_word(const __nv_bfloat16* p) { return *reinterpret_cast<const unsigned*>(p); }
-
-__device__ __forceinline__ void lc_split(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
-  hi = __float2bfloat16_rn(v);
-  lo = __float2bfloat16_rn(v - __bfloat162float(hi));
-}
-
-struct Bf16x8 { __nv_bfloat16 v[8]; };
-__device__ __forceinline__ Bf16x8 lc_load8(const __nv_bfloat16* p, bool live) {
-  Bf16x8 r;
-  uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-  if (live) raw = *reinterpret_cast<const uint4*>(p);
-  *reinterpret_cast<uint4*>(r.v) = raw;
-  return r;
-}
-
 // columns [begin, begin + count) of every row: x <- SiLU(x), rounded once; eight values a thread
 __global__ void lightning_activate_kernel(__nv_bfloat16* proj, long long pitch, int rows, int begin0, int count0, int begin1,
                                           int count1, int begin2, int count2) {
@@ -378,40 +360,6 @@ __global__ void lightning_activate_kernel(__nv_bfloat16* proj, long long pitch, 
   }
 }
 
-// Loads a [LC_TOKENS, WIDTH] slice of the (activated) projection, transposed, into `dst` [WIDTH][TP]: consecutive lanes
-// take consecutive tokens, so the 2-byte stores of a warp fall into consecutive words.  `scale` (or null) gives a
-// factor per token; with it the product goes in as two bfloat16 numbers (dst, dst_lo).
-template <int WIDTH, int THREADS>
-__device__ __forceinline__ void lc_load_transposed(const __nv_bfloat16* src, long long pitch, int n, const float* scale,
-                                                   int scale_last, __nv_bfloat16* dst, __nv_bfloat16* dst_lo) {
-  constexpr int TP = LC_TOKENS + LC_PAD, ITEMS = LC_TOKENS * WIDTH / 8, PER = ITEMS / THREADS, BATCH = PER < 8 ? PER : 8;
-#pragma unroll 1
-  for (int first = 0; first < PER; first += BATCH) {          // eight loads of a thread in flight at a time
-    Bf16x8 x[BATCH];
-#pragma unroll
-    for (int i = 0; i < BATCH; ++i) {
-      const int item = threadIdx.x + (first + i) * THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
-      x[i] = lc_load8(src + (size_t)j * pitch + d0, j < n);
-    }
-#pragma unroll
-    for (int i = 0; i < BATCH; ++i) {
-      const int item = threadIdx.x + (first + i) * THREADS, j = item % LC_TOKENS, d0 = item / LC_TOKENS * 8;
-      const float factor = (scale && j < n) ? scale[scale_last - j] : 0.f;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        if (scale) {
-          __nv_bfloat16 hi, lo;
-          lc_split(factor * __bfloat162float(x[i].v[k]), hi, lo);
-          dst[(d0 + k) * TP + j] = hi;
-          dst_lo[(d0 + k) * TP + j] = lo;
-        } else {
-          dst[(d0 + k) * TP + j] = x[i].v[k];
-        }
-      }
-    }
-  }
-}
-
 template <int DIM, int VDIM>
 __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_states_kernel(LightningChunkArgs a) {
   constexpr int TP = LC_TOKENS + LC_PAD;
@@ -427,8 +375,8 @@ __global__ void __launch_bounds__(LC_THREADS) lightning_chunk_states_kernel(Ligh
   int request, row0, n;
   if (!lc_find(a, blockIdx.x, request, row0, n)) return;
   __syncthreads();
-  lc_load_transposed<DIM, LC_THREADS>(a.proj + (size_t)row0 * a.pitch + a.k_offset + head * DIM, a.pitch, n, power, n - 1, kt_hi, kt_lo);
-  lc_load_transposed<VDIM, LC_THREADS>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
+  lc_load_transposed<DIM, LC_THREADS>(a.proj + (size_t)row0 * a.pitch + a.k_offset + head * DIM, a.pitch, n, power, n - 1, -1, kt_hi, kt_lo);
+  lc_load_transposed<VDIM, LC_THREADS>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, 0, vt, nullptr);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   constexpr int MT = DIM / 64;                 // m16 tiles per warp: the warp owns DIM / 4 rows of U
@@ -545,7 +493,7 @@ __global__ void __launch_bounds__(LC_OUT_THREADS) lightning_chunk_outputs_kernel
       *reinterpret_cast<uint4*>(ks + j * DP + d0) = *reinterpret_cast<const uint4*>(xk[i].v);
     }
   }
-  lc_load_transposed<VDIM, LC_OUT_THREADS>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, vt, nullptr);
+  lc_load_transposed<VDIM, LC_OUT_THREADS>(a.proj + (size_t)row0 * a.pitch + a.v_offset + head * VDIM, a.pitch, n, nullptr, 0, 0, vt, nullptr);
   {
     // the state before the chunk, [d][c] floats, into [c][d] as two bfloat16 numbers: consecutive lanes take
     // consecutive d, four columns each

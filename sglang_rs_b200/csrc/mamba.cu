@@ -42,18 +42,18 @@ struct MambaShape {
 __device__ __forceinline__ float mamba_silu(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float mamba_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-template <typename T>
+template <typename T, typename O>
 __global__ void mamba_conv_kernel(const T* __restrict__ proj, const float* __restrict__ weight, const float* __restrict__ bias,
                                   const int* __restrict__ positions, const int* __restrict__ row_request,
                                   const int* __restrict__ cu_rows, const int* __restrict__ state_slots,
-                                  const float* __restrict__ state, float* __restrict__ out, MambaShape s) {
+                                  const float* __restrict__ state, O* __restrict__ out, MambaShape s) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int row = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= s.channels) return;
   const int pos = positions[row];
-  float* dst = out + (size_t)row * s.channels + c;
-  if (pos < 0) { *dst = 0.f; return; }
+  O* dst = out + (size_t)row * s.channels + c;
+  if (pos < 0) { *dst = srb_from_float<O>(0.f); return; }
   const int request = row_request[row];
   const int ahead = row - cu_rows[request];            // rows of this request before this one in the step
   const float* kept = state + (size_t)state_slots[request] * s.slot_floats;
@@ -68,7 +68,7 @@ __global__ void mamba_conv_kernel(const T* __restrict__ proj, const float* __res
       u = kept[(size_t)(s.taps - 1 - (back - ahead)) * s.channels + c];
     acc = fmaf(weight[(size_t)c * s.taps + j], u, acc);
   }
-  *dst = mamba_silu(acc);
+  *dst = srb_from_float<O>(mamba_silu(acc));
 }
 
 // One thread per (request, channel): the slot's inputs become the last taps - 1 of the sequence after this step.
@@ -223,35 +223,42 @@ extern "C" long long srb_mamba_slot_floats(int heads, int vdim, int nstate, int 
   return (long long)(taps - 1) * (heads * vdim + 2 * groups * nstate) + (long long)heads * nstate * vdim;
 }
 
-// proj: [rows, pitch]; weight [channels, taps], bias [channels] (float); out: float [rows, channels]
+template <typename T, typename O>
+static int launch_mamba_conv(const void* proj, const float* weight, const float* bias, const int* positions,
+                             const int* row_request, const int* cu_rows, const int* state_slots, float* state, void* out,
+                             int rows, int requests, int write_state, const MambaShape& s, cudaStream_t st) {
+  const int block = 128;
+  const dim3 grid(rows, (s.channels + block - 1) / block), keep_grid((s.channels + block - 1) / block, requests);
+  SRB_CUDA_CALL(srb_launch(mamba_conv_kernel<T, O>, grid, dim3(block), 0, st, (const T*)proj, weight, bias, positions,
+                           row_request, cu_rows, state_slots, (const float*)state, (O*)out, s));
+  if (write_state && s.taps > 1)
+    SRB_CUDA_CALL(srb_launch(mamba_conv_keep_kernel<T>, keep_grid, dim3(block), 0, st, (const T*)proj, positions, cu_rows,
+                             state_slots, state, s));
+  SRB_LAUNCH_CHECK("mamba_conv");
+  return SRB_OK;
+}
+
+// proj: [rows, pitch]; weight [channels, taps], bias [channels] (float); out: [rows, channels] of `out_dtype` (float,
+// or bfloat16 beside a bfloat16 projection: what the chunk kernels read)
 extern "C" int srb_mamba_conv(const void* proj, long long proj_pitch, const float* weight, const float* bias,
                               const int* positions, const int* row_request, const int* cu_rows, const int* state_slots,
-                              float* state, long long slot_floats, float* out, int rows, int requests, int heads, int vdim,
-                              int nstate, int groups, int taps, int write_state, int dtype, void* stream) {
+                              float* state, long long slot_floats, void* out, int rows, int requests, int heads, int vdim,
+                              int nstate, int groups, int taps, int write_state, int dtype, int out_dtype, void* stream) {
   if (rows <= 0 || requests <= 0) return SRB_OK;
   MambaShape s;
   if (mamba_shape(s, heads, vdim, nstate, groups, taps, proj_pitch, slot_floats) != SRB_OK) return SRB_ERR_INVALID;
   if (requests > 65535) SRB_FAIL("mamba_conv: %d requests exceed one launch", requests);
   cudaStream_t st = (cudaStream_t)stream;
-  const int block = 128;
-  const dim3 grid(rows, (s.channels + block - 1) / block), keep_grid((s.channels + block - 1) / block, requests);
-  if (dtype == SRB_DTYPE_F32) {
-    SRB_CUDA_CALL(srb_launch(mamba_conv_kernel<float>, grid, dim3(block), 0, st, (const float*)proj, weight, bias, positions,
-                             row_request, cu_rows, state_slots, (const float*)state, out, s));
-    if (write_state && taps > 1)
-      SRB_CUDA_CALL(srb_launch(mamba_conv_keep_kernel<float>, keep_grid, dim3(block), 0, st, (const float*)proj, positions,
-                               cu_rows, state_slots, state, s));
-  } else if (dtype == SRB_DTYPE_BF16) {
-    SRB_CUDA_CALL(srb_launch(mamba_conv_kernel<__nv_bfloat16>, grid, dim3(block), 0, st, (const __nv_bfloat16*)proj, weight,
-                             bias, positions, row_request, cu_rows, state_slots, (const float*)state, out, s));
-    if (write_state && taps > 1)
-      SRB_CUDA_CALL(srb_launch(mamba_conv_keep_kernel<__nv_bfloat16>, keep_grid, dim3(block), 0, st,
-                               (const __nv_bfloat16*)proj, positions, cu_rows, state_slots, state, s));
-  } else {
-    SRB_FAIL("mamba_conv: unknown dtype %d", dtype);
-  }
-  SRB_LAUNCH_CHECK("mamba_conv");
-  return SRB_OK;
+  if (dtype == SRB_DTYPE_F32 && out_dtype == SRB_DTYPE_F32)
+    return launch_mamba_conv<float, float>(proj, weight, bias, positions, row_request, cu_rows, state_slots, state, out, rows,
+                                           requests, write_state, s, st);
+  if (dtype == SRB_DTYPE_BF16 && out_dtype == SRB_DTYPE_F32)
+    return launch_mamba_conv<__nv_bfloat16, float>(proj, weight, bias, positions, row_request, cu_rows, state_slots, state, out,
+                                                   rows, requests, write_state, s, st);
+  if (dtype == SRB_DTYPE_BF16 && out_dtype == SRB_DTYPE_BF16)
+    return launch_mamba_conv<__nv_bfloat16, __nv_bfloat16>(proj, weight, bias, positions, row_request, cu_rows, state_slots, state,
+                                                           out, rows, requests, write_state, s, st);
+  SRB_FAIL("mamba_conv: a projection of dtype %d with a result of dtype %d is not taken", dtype, out_dtype);
 }
 
 template <typename T>
@@ -316,4 +323,382 @@ extern "C" int srb_mamba_gate_norm(const float* y, const void* proj, long long p
   }
   SRB_LAUNCH_CHECK("mamba_gate_norm");
   return SRB_OK;
+}
+
+// ---- prompt portions in bfloat16: chunks in parallel, products on the tensor cores -------------------------------
+// The rows of every request are cut into chunks of LC_TOKENS (128) tokens (from the request's first row of the step).
+// With c_t = sum_(i <= t) -exp(A_log) dt_i taken inside the chunk (never positive, so no exponential exceeds 1), a
+// chunk that starts from state S and holds tokens 0 .. n-1 has
+//     y_t = exp(c_t) S^T C_t + sum_(j <= t) exp(c_t - c_j) dt_j (C_t . B_j) x_j + D x_t
+//     S  <- exp(c_(n-1)) S + sum_j exp(c_(n-1) - c_j) dt_j B_j x_j^T
+// Three kernels behind the convolution (which here rounds its result to bfloat16):
+//   1. per (chunk, head) the chunk's own contribution to the state, U, and exp(c_(n-1))                   (parallel)
+//   2. per (request, head, entry) the states before every chunk, walking the request's chunks in order; U is replaced
+//      by the state before the chunk, and the request's slot receives the last state                      (cheap)
+//   3. per (chunk, head) the results                                                                       (parallel)
+// x, B and C go in as bfloat16 (mma.sync m16n8k16, 32-bit accumulation); step sizes, sums of logarithms of decays and
+// exponentials are 32-bit; whatever is 32-bit by the design and has to be an operand of a product (B times its factor,
+// decayed scores, the state) goes in as the sum of two bfloat16 numbers in two products.  The state and U lie as
+// [heads][P][N], as in a request's slot.
+#include "chunk_helpers.cuh"
+#define MC_THREADS 128
+#define MC_OUT_THREADS (LC_TOKENS * 2)      // the results kernel: a warp per sixteen rows of the chunk
+
+struct MambaChunkArgs {
+  const __nv_bfloat16* proj;   // [rows, pitch]: the dt entries are read
+  const __nv_bfloat16* xbc;    // [rows, channels]: what the convolution wrote
+  const float* a_log;
+  const float* d_skip;
+  const float* dt_bias;
+  const int* cu_rows;
+  const int* positions;
+  const int* state_slots;
+  float* state;
+  float* chunk_states;         // [chunks, heads, P, N]: U of a chunk, then the state before it
+  float* chunk_decay;          // [chunks, heads]: exp(c_(n-1))
+  float* y;                    // [rows, inner]
+  int requests, write_state;
+  MambaShape s;
+};
+
+// the request and the chunk of it that block `index` works on; false: there is no such chunk
+__device__ __forceinline__ bool mc_find(const MambaChunkArgs& a, int index, int& request, int& row0, int& n) {
+  int first = 0;
+  for (request = 0; request < a.requests; ++request) {
+    const int begin = a.cu_rows[request], rows = a.cu_rows[request + 1] - begin;
+    const int chunks = (rows + LC_TOKENS - 1) / LC_TOKENS;
+    if (index < first + chunks) {
+      row0 = begin + (index - first) * LC_TOKENS;
+      n = min(LC_TOKENS, begin + rows - row0);
+      return true;
+    }
+    first += chunks;
+  }
+  return false;
+}
+
+// dt_s[j] = softplus(dt_j + bias) and cum_s[j] = c_j for the chunk's tokens (beyond the n-th: 0, and c stays); every
+// thread of the block comes here, and the block has at least LC_TOKENS threads
+__device__ __forceinline__ void mc_steps(const MambaChunkArgs& a, int head, int row0, int n, float* dt_s, float* cum_s) {
+  const int tid = threadIdx.x;
+  if (tid < LC_TOKENS) {
+    float dt = 0.f;
+    if (tid < n) {
+      const size_t at = (size_t)(row0 + tid) * a.s.proj_pitch + a.s.inner + a.s.channels + head;
+      dt = mamba_softplus(__bfloat162float(a.proj[at]) + a.dt_bias[head]);
+    }
+    dt_s[tid] = dt;
+    cum_s[tid] = -expf(a.a_log[head]) * dt;
+  }
+  __syncthreads();
+  if (tid < 32) {                      // a lane sums four consecutive tokens, the lanes' totals are scanned
+    float part[LC_TOKENS / 32], sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < LC_TOKENS / 32; ++k) {
+      sum += cum_s[tid * (LC_TOKENS / 32) + k];
+      part[k] = sum;
+    }
+    float total = sum;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const float other = __shfl_up_sync(0xffffffffu, total, offset);
+      if (tid >= offset) total += other;
+    }
+    float before = __shfl_up_sync(0xffffffffu, total, 1);
+    if (tid == 0) before = 0.f;
+#pragma unroll
+    for (int k = 0; k < LC_TOKENS / 32; ++k) cum_s[tid * (LC_TOKENS / 32) + k] = before + part[k];
+  }
+  __syncthreads();
+}
+
+template <int N, int P>
+__global__ void __launch_bounds__(MC_THREADS) mamba_chunk_states_kernel(MambaChunkArgs a) {
+  constexpr int TP = LC_TOKENS + LC_PAD;
+  extern __shared__ __align__(16) unsigned char mc_smem[];
+  __nv_bfloat16* xt = reinterpret_cast<__nv_bfloat16*>(mc_smem);         // [P][TP]
+  __nv_bfloat16* bt_hi = xt + P * TP;                                    // [N][TP]: exp(c_(n-1) - c_j) dt_j B_j, rounded
+  __nv_bfloat16* bt_lo = bt_hi + N * TP;                                 // ... and what the rounding left
+  __shared__ float dt_s[LC_TOKENS], cum_s[LC_TOKENS], w_s[LC_TOKENS];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int head = blockIdx.y;
+  int request, row0, n;
+  if (!mc_find(a, blockIdx.x, request, row0, n)) return;
+  mc_steps(a, head, row0, n, dt_s, cum_s);
+  if (threadIdx.x < LC_TOKENS) w_s[threadIdx.x] = threadIdx.x < n ? expf(cum_s[n - 1] - cum_s[threadIdx.x]) * dt_s[threadIdx.x] : 0.f;
+  __syncthreads();
+  const int group = head / (a.s.heads / a.s.groups);
+  const __nv_bfloat16* rows = a.xbc + (size_t)row0 * a.s.channels;
+  lc_load_transposed<P, MC_THREADS>(rows + head * P, a.s.channels, n, nullptr, 0, 0, xt, nullptr);
+  lc_load_transposed<N, MC_THREADS>(rows + a.s.inner + group * N, a.s.channels, n, w_s, 0, 1, bt_hi, bt_lo);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr int MT = P / 64;                   // m16 tiles per warp: the warp owns P / 4 rows of U
+  constexpr int NT = N / 8;
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) acc[m][nt][0] = acc[m][nt][1] = acc[m][nt][2] = acc[m][nt][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < LC_TOKENS / 16; ++kk) {
+    unsigned ax[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const int row = warp * (P / 4) + m * 16 + g, col = kk * 16 + 2 * t;
+      ax[m][0] = lc_word(xt + row * TP + col);
+      ax[m][1] = lc_word(xt + (row + 8) * TP + col);
+      ax[m][2] = lc_word(xt + row * TP + col + 8);
+      ax[m][3] = lc_word(xt + (row + 8) * TP + col + 8);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int at = (nt * 8 + g) * TP + kk * 16 + 2 * t;
+      const unsigned h0 = lc_word(bt_hi + at), h1 = lc_word(bt_hi + at + 8);
+      const unsigned l0 = lc_word(bt_lo + at), l1 = lc_word(bt_lo + at + 8);
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        mma_bf16(acc[m][nt], ax[m], h0, h1);
+        mma_bf16(acc[m][nt], ax[m], l0, l1);
+      }
+    }
+  }
+  float* u = a.chunk_states + ((size_t)blockIdx.x * a.s.heads + head) * N * P;
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int row = warp * (P / 4) + m * 16 + g, col = nt * 8 + 2 * t;
+      *reinterpret_cast<float2*>(u + (size_t)row * N + col) = make_float2(acc[m][nt][0], acc[m][nt][1]);
+      *reinterpret_cast<float2*>(u + (size_t)(row + 8) * N + col) = make_float2(acc[m][nt][2], acc[m][nt][3]);
+    }
+  if (threadIdx.x == 0) a.chunk_decay[(size_t)blockIdx.x * a.s.heads + head] = expf(cum_s[n - 1]);
+}
+
+// One thread per entry of a head's state: the request's chunks in order.
+__global__ void mamba_chunk_prefix_kernel(MambaChunkArgs a, int entries) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x, head = blockIdx.y, request = blockIdx.z;
+  if (e >= entries) return;
+  int first = 0;
+  for (int r = 0; r < request; ++r) first += (a.cu_rows[r + 1] - a.cu_rows[r] + LC_TOKENS - 1) / LC_TOKENS;
+  const int begin = a.cu_rows[request], rows = a.cu_rows[request + 1] - begin;
+  if (rows <= 0) return;
+  const int start = a.positions[begin];
+  if (start < 0) return;
+  float* state = a.state + (size_t)a.state_slots[request] * a.s.slot_floats + a.s.conv_floats + (size_t)head * entries + e;
+  float s = start == 0 ? 0.f : *state;
+  const int chunks = (rows + LC_TOKENS - 1) / LC_TOKENS;
+  const size_t step = (size_t)a.s.heads * entries;
+  float* u = a.chunk_states + ((size_t)first * a.s.heads + head) * entries + e;
+  const float* decay = a.chunk_decay + (size_t)first * a.s.heads + head;
+  for (int c0 = 0; c0 < chunks; c0 += 8) {
+    float own[8], factor[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (c0 + k < chunks) {                                           // the loads of eight chunks in flight
+        own[k] = u[(size_t)(c0 + k) * step];
+        factor[k] = decay[(size_t)(c0 + k) * a.s.heads];
+      }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int c = c0 + k;
+      if (c >= chunks) break;
+      u[(size_t)c * step] = s;
+      s = fmaf(factor[k], s, own[k]);
+    }
+  }
+  if (a.write_state) *state = s;
+}
+
+template <int N, int P>
+__global__ void __launch_bounds__(MC_OUT_THREADS) mamba_chunk_outputs_kernel(MambaChunkArgs a) {
+  constexpr int DP = N + LC_PAD, TP = LC_TOKENS + LC_PAD;
+  extern __shared__ __align__(16) unsigned char mc_smem[];
+  __nv_bfloat16* cs = reinterpret_cast<__nv_bfloat16*>(mc_smem);          // [LC_TOKENS][DP]: C_t
+  __nv_bfloat16* bs = cs + LC_TOKENS * DP;                                // [LC_TOKENS][DP]: B_j
+  __nv_bfloat16* xt = bs + LC_TOKENS * DP;                                // [P][TP]
+  __nv_bfloat16* st_hi = xt + P * TP;                                     // [P][DP]: the state before the chunk
+  __nv_bfloat16* st_lo = st_hi + P * DP;
+  __shared__ float dt_s[LC_TOKENS], cum_s[LC_TOKENS];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int head = blockIdx.y;
+  int request, row0, n;
+  if (!mc_find(a, blockIdx.x, request, row0, n)) return;
+  mc_steps(a, head, row0, n, dt_s, cum_s);
+  const int group = head / (a.s.heads / a.s.groups);
+  const __nv_bfloat16* rows = a.xbc + (size_t)row0 * a.s.channels;
+  {
+    // B and C as they lie: 16-byte pieces, a row's pieces in consecutive lanes
+    constexpr int PIECES = LC_TOKENS * N / 8, PER = PIECES / MC_OUT_THREADS;
+    const int c_from_b = a.s.groups * N;
+    Bf16x8 xc[PER], xb[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int piece = threadIdx.x + i * MC_OUT_THREADS, j = piece / (N / 8), d0 = piece % (N / 8) * 8;
+      const __nv_bfloat16* row = rows + (size_t)j * a.s.channels + a.s.inner + group * N + d0;
+      xb[i] = lc_load8(row, j < n);
+      xc[i] = lc_load8(row + c_from_b, j < n);
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int piece = threadIdx.x + i * MC_OUT_THREADS, j = piece / (N / 8), d0 = piece % (N / 8) * 8;
+      *reinterpret_cast<uint4*>(cs + j * DP + d0) = *reinterpret_cast<const uint4*>(xc[i].v);
+      *reinterpret_cast<uint4*>(bs + j * DP + d0) = *reinterpret_cast<const uint4*>(xb[i].v);
+    }
+  }
+  lc_load_transposed<P, MC_OUT_THREADS>(rows + head * P, a.s.channels, n, nullptr, 0, 0, xt, nullptr);
+  {
+    // the state before the chunk, [p][n] floats, as two bfloat16 numbers: four entries of a column a thread
+    const float* before = a.chunk_states + ((size_t)blockIdx.x * a.s.heads + head) * N * P;
+    constexpr int ITEMS = N * P / 4, BATCH = 8;
+    for (int first = 0; first < ITEMS; first += BATCH * MC_OUT_THREADS) {
+      float4 x[BATCH];
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int item = first + threadIdx.x + i * MC_OUT_THREADS;
+        x[i] = item < ITEMS ? *reinterpret_cast<const float4*>(before + (size_t)item * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < BATCH; ++i) {
+        const int item = first + threadIdx.x + i * MC_OUT_THREADS, p = item / (N / 4), n0 = item % (N / 4) * 4;
+        if (item >= ITEMS) continue;
+        const float v[4] = {x[i].x, x[i].y, x[i].z, x[i].w};
+        __nv_bfloat16 hi[4], lo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) lc_split(v[k], hi[k], lo[k]);
+        *reinterpret_cast<uint2*>(st_hi + p * DP + n0) = *reinterpret_cast<const uint2*>(hi);
+        *reinterpret_cast<uint2*>(st_lo + p * DP + n0) = *reinterpret_cast<const uint2*>(lo);
+      }
+    }
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  constexpr int NT = P / 8, ST = LC_TOKENS / 8;
+  const int r0 = warp * 16 + g, r1 = r0 + 8;              // this thread's two rows (tokens) of the chunk
+  // what the state before the chunk gives: C_t S, then times exp(c_t)
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  float score[ST][4];
+#pragma unroll
+  for (int nt = 0; nt < ST; ++nt) score[nt][0] = score[nt][1] = score[nt][2] = score[nt][3] = 0.f;
+#pragma unroll 2
+  for (int kk = 0; kk < N / 16; ++kk) {
+    unsigned qa[4];
+    const int col = kk * 16 + 2 * t;
+    qa[0] = lc_word(cs + r0 * DP + col);
+    qa[1] = lc_word(cs + r1 * DP + col);
+    qa[2] = lc_word(cs + r0 * DP + col + 8);
+    qa[3] = lc_word(cs + r1 * DP + col + 8);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int at = (nt * 8 + g) * DP + col;
+      mma_bf16(acc[nt], qa, lc_word(st_hi + at), lc_word(st_hi + at + 8));
+      mma_bf16(acc[nt], qa, lc_word(st_lo + at), lc_word(st_lo + at + 8));
+    }
+#pragma unroll
+    for (int nt = 0; nt < ST; ++nt) {
+      const int at = (nt * 8 + g) * DP + col;
+      mma_bf16(score[nt], qa, lc_word(bs + at), lc_word(bs + at + 8));
+    }
+  }
+  const float cum0 = cum_s[r0], cum1 = cum_s[r1];
+  const float carry0 = expf(cum0), carry1 = expf(cum1);
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    acc[nt][0] *= carry0; acc[nt][1] *= carry0;
+    acc[nt][2] *= carry1; acc[nt][3] *= carry1;
+  }
+  // the chunk's own tokens: decayed scores of the tokens up to the row's own, times their steps, as two bfloat16 operands
+#pragma unroll
+  for (int kj = 0; kj < LC_TOKENS / 16; ++kj) {
+    unsigned hi[4], lo[4];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int nt = 2 * kj + half, j0 = nt * 8 + 2 * t;
+      float v[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = c < 2 ? r0 : r1, j = j0 + (c & 1);
+        v[c] = (j <= r && r < n) ? score[nt][c] * (expf((c < 2 ? cum0 : cum1) - cum_s[j]) * dt_s[j]) : 0.f;
+      }
+      __nv_bfloat16 h[4], l[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) lc_split(v[c], h[c], l[c]);
+      hi[half * 2] = pack_bf16(__bfloat162float(h[0]), __bfloat162float(h[1]));
+      hi[half * 2 + 1] = pack_bf16(__bfloat162float(h[2]), __bfloat162float(h[3]));
+      lo[half * 2] = pack_bf16(__bfloat162float(l[0]), __bfloat162float(l[1]));
+      lo[half * 2 + 1] = pack_bf16(__bfloat162float(l[2]), __bfloat162float(l[3]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const __nv_bfloat16* b = xt + (nt * 8 + g) * TP + kj * 16 + 2 * t;
+      const unsigned b0 = lc_word(b), b1 = lc_word(b + 8);
+      mma_bf16(acc[nt], hi, b0, b1);
+      mma_bf16(acc[nt], lo, b0, b1);
+    }
+  }
+  const float skip = a.d_skip[head];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const int c = nt * 8 + 2 * t;
+    float* out = a.y + (size_t)row0 * a.s.inner + head * P + c;
+    if (r0 < n)
+      *reinterpret_cast<float2*>(out + (size_t)r0 * a.s.inner) =
+          make_float2(fmaf(skip, __bfloat162float(xt[c * TP + r0]), acc[nt][0]), fmaf(skip, __bfloat162float(xt[(c + 1) * TP + r0]), acc[nt][1]));
+    if (r1 < n)
+      *reinterpret_cast<float2*>(out + (size_t)r1 * a.s.inner) =
+          make_float2(fmaf(skip, __bfloat162float(xt[c * TP + r1]), acc[nt][2]), fmaf(skip, __bfloat162float(xt[(c + 1) * TP + r1]), acc[nt][3]));
+  }
+}
+
+template <int N, int P>
+static int launch_mamba_chunks(const MambaChunkArgs& a, int chunks, cudaStream_t st) {
+  const size_t smem1 = (size_t)(2 * N + P) * (LC_TOKENS + LC_PAD) * 2;
+  const size_t smem3 = ((size_t)2 * LC_TOKENS * (N + LC_PAD) + (size_t)P * (LC_TOKENS + LC_PAD) + (size_t)2 * P * (N + LC_PAD)) * 2;
+  SRB_CUDA_CALL(cudaFuncSetAttribute(mamba_chunk_states_kernel<N, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1));
+  SRB_CUDA_CALL(cudaFuncSetAttribute(mamba_chunk_outputs_kernel<N, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3));
+  SRB_CUDA_CALL(srb_launch(mamba_chunk_states_kernel<N, P>, dim3(chunks, a.s.heads), dim3(MC_THREADS), smem1, st, a));
+  SRB_LAUNCH_CHECK("mamba_chunk_states");
+  const int entries = N * P;
+  SRB_CUDA_CALL(srb_launch(mamba_chunk_prefix_kernel, dim3((entries + 255) / 256, a.s.heads, a.requests), dim3(256), 0, st, a, entries));
+  SRB_LAUNCH_CHECK("mamba_chunk_prefix");
+  SRB_CUDA_CALL(srb_launch(mamba_chunk_outputs_kernel<N, P>, dim3(chunks, a.s.heads), dim3(MC_OUT_THREADS), smem3, st, a));
+  SRB_LAUNCH_CHECK("mamba_chunk_outputs");
+  return SRB_OK;
+}
+
+// Tokens of a chunk, and whether these sizes are taken (bfloat16; N and P 64 or 128 each).
+extern "C" int srb_mamba_chunk_tokens() { return LC_TOKENS; }
+extern "C" int srb_mamba_chunks_supports(int vdim, int nstate, int dtype) {
+  return dtype == SRB_DTYPE_BF16 && (nstate == 64 || nstate == 128) && (vdim == 64 || vdim == 128);
+}
+
+// What srb_mamba_scan computes, for prompt portions in bfloat16.  `xbc`: bfloat16 [rows, channels] (srb_mamba_conv with a
+// bfloat16 result); `chunks`: at least the number of chunks of the step, sum over the requests of ceil(rows /
+// srb_mamba_chunk_tokens()); `scratch`: chunks * heads * (N * P + 1) floats.
+extern "C" int srb_mamba_chunks(const void* proj, long long proj_pitch, const void* xbc, const float* a_log, const float* d_skip,
+                                const float* dt_bias, const int* positions, const int* cu_rows, const int* state_slots,
+                                float* state, long long slot_floats, float* scratch, float* y, int rows, int requests, int chunks,
+                                int heads, int vdim, int nstate, int groups, int taps, int write_state, void* stream) {
+  if (rows <= 0 || requests <= 0 || chunks <= 0) return SRB_OK;
+  MambaChunkArgs a;
+  if (mamba_shape(a.s, heads, vdim, nstate, groups, taps, proj_pitch, slot_floats) != SRB_OK) return SRB_ERR_INVALID;
+  if (!srb_mamba_chunks_supports(vdim, nstate, SRB_DTYPE_BF16))
+    SRB_FAIL("mamba_chunks: a state of %d x %d per head is not taken (64 or 128 each)", nstate, vdim);
+  if (heads > 65535 || requests > 65535) SRB_FAIL("mamba_chunks: %d heads or %d requests exceed one launch", heads, requests);
+  if (((uintptr_t)xbc & 15) || ((uintptr_t)scratch & 15)) SRB_FAIL("mamba_chunks: the convolved inputs and the scratch must start on 16-byte borders");
+  a.proj = (const __nv_bfloat16*)proj; a.xbc = (const __nv_bfloat16*)xbc; a.a_log = a_log; a.d_skip = d_skip; a.dt_bias = dt_bias;
+  a.cu_rows = cu_rows; a.positions = positions; a.state_slots = state_slots; a.state = state;
+  a.chunk_states = scratch; a.chunk_decay = scratch + (size_t)chunks * heads * nstate * vdim; a.y = y;
+  a.requests = requests; a.write_state = write_state;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (nstate == 64 && vdim == 64) return launch_mamba_chunks<64, 64>(a, chunks, st);
+  if (nstate == 64) return launch_mamba_chunks<64, 128>(a, chunks, st);
+  if (vdim == 64) return launch_mamba_chunks<128, 64>(a, chunks, st);
+  return launch_mamba_chunks<128, 128>(a, chunks, st);
 }

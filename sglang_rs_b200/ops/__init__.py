@@ -1257,12 +1257,14 @@ def mamba_conv(proj: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, pos
                cu_rows: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor, num_requests: int, *,
                heads: int, vdim: int, nstate: int, groups: int, taps: int, read_only: bool = False) -> None:
     """The causal convolution per channel and SiLU of the x, B and C entries of ``proj``'s rows
-    ([z | x | B | C | dt]); ``out`` float32 [rows, channels].  Inputs before a request's first row of the step come from
+    ([z | x | B | C | dt]); ``out`` [rows, channels], float32 or (beside a bfloat16 ``proj``, for :func:`mamba_chunks`)
+    bfloat16.  Inputs before a request's first row of the step come from
     its slot of ``state`` (zeros before position 0); unless ``read_only`` the slot then keeps the sequence's last
     ``taps`` - 1 inputs.  ``weight`` float32 [channels, taps] (the last column is the current token's), ``bias`` [channels]."""
     _mamba_args(proj, state, heads, vdim, nstate, groups, taps)
     channels = heads * vdim + 2 * groups * nstate
-    _need(weight, "weight", torch.float32); _need(bias, "bias", torch.float32); _need(out, "out", torch.float32)
+    _need(weight, "weight", torch.float32); _need(bias, "bias", torch.float32)
+    _need(out, "out", torch.float32 if out.dtype != proj.dtype else proj.dtype)
     for name, t in (("positions", positions), ("row_request", row_request), ("cu_rows", cu_rows), ("state_slots", state_slots)):
         _need(t, name, torch.int32)
     rows = proj.shape[0]
@@ -1272,7 +1274,7 @@ def mamba_conv(proj: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, pos
     _check(lib, lib.srb_mamba_conv(_ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(weight), _ptr(bias), _ptr(positions),
                                    _ptr(row_request), _ptr(cu_rows), _ptr(state_slots), _ptr(state),
                                    ctypes.c_longlong(state.stride(0)), _ptr(out), rows, int(num_requests), heads, vdim, nstate,
-                                   groups, taps, int(not read_only), dtype_code(proj.dtype), _stream()),
+                                   groups, taps, int(not read_only), dtype_code(proj.dtype), dtype_code(out.dtype), _stream()),
            launches=1 if read_only or taps == 1 else 2)
 
 
@@ -1298,6 +1300,46 @@ def mamba_scan(proj: torch.Tensor, xbc: torch.Tensor, a_log: torch.Tensor, d_ski
                                    _ptr(dt_bias), _ptr(positions), _ptr(cu_rows), _ptr(state_slots), _ptr(state),
                                    ctypes.c_longlong(state.stride(0)), _ptr(y), rows, int(num_requests), heads, vdim, nstate, groups,
                                    taps, int(not read_only), dtype_code(proj.dtype), _stream()))
+
+
+def mamba_chunks_takes(dtype: torch.dtype, vdim: int, nstate: int) -> bool:
+    """True if the tensor-core kernels for prompt portions take these sizes (the rule of srb_mamba_chunks_supports)."""
+    return dtype == torch.bfloat16 and vdim in (64, 128) and nstate in (64, 128)
+
+
+#: tokens per chunk of :func:`mamba_chunks` (LC_TOKENS of csrc/chunk_helpers.cuh)
+MAMBA_CHUNK_TOKENS = 128
+
+
+@traced("mamba_scan")
+def mamba_chunks(proj: torch.Tensor, xbc: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, dt_bias: torch.Tensor,
+                 positions: torch.Tensor, cu_rows: torch.Tensor, state_slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor,
+                 num_requests: int, chunks: int, *, heads: int, vdim: int, nstate: int, groups: int, taps: int,
+                 read_only: bool = False) -> None:
+    """What :func:`mamba_scan` computes, for prompt portions in bfloat16: the rows of every request are cut into chunks
+    of ``MAMBA_CHUNK_TOKENS`` tokens that run in parallel on the tensor cores (each chunk's own contribution to the
+    state, then the states before every chunk in order, then the results).  ``xbc``: bfloat16, what :func:`mamba_conv`
+    wrote; ``chunks``: the number of chunks of the step, sum over the requests of ceil(rows / MAMBA_CHUNK_TOKENS), or more."""
+    _mamba_args(proj, state, heads, vdim, nstate, groups, taps)
+    rows, inner = proj.shape[0], heads * vdim
+    _need(proj, "proj", torch.bfloat16); _need(xbc, "xbc", torch.bfloat16); _need(y, "y", torch.float32)
+    for name, t in (("a_log", a_log), ("d_skip", d_skip), ("dt_bias", dt_bias)):
+        _need(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"mamba_chunks: {name} needs one entry per head")
+    for name, t in (("positions", positions), ("cu_rows", cu_rows), ("state_slots", state_slots)):
+        _need(t, name, torch.int32)
+    if xbc.shape != (rows, inner + 2 * groups * nstate) or not xbc.is_contiguous() or y.shape != (rows, inner):
+        raise KernelError("mamba_chunks: shapes of the convolved inputs and the output do not agree")
+    if not mamba_chunks_takes(proj.dtype, vdim, nstate):
+        raise KernelError(f"mamba_chunks: a state of {nstate} x {vdim} per head is not taken")
+    chunks = max(int(chunks), 1)
+    scratch = torch.empty((chunks * heads * (nstate * vdim + 1),), dtype=torch.float32, device=proj.device)
+    lib = load_library("mamba")
+    _check(lib, lib.srb_mamba_chunks(_ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(xbc), _ptr(a_log), _ptr(d_skip),
+                                     _ptr(dt_bias), _ptr(positions), _ptr(cu_rows), _ptr(state_slots), _ptr(state),
+                                     ctypes.c_longlong(state.stride(0)), _ptr(scratch), _ptr(y), rows, int(num_requests), chunks,
+                                     heads, vdim, nstate, groups, taps, int(not read_only), _stream()), launches=3)
 
 
 @traced("mamba_gate_norm")

@@ -39,6 +39,9 @@ class MambaNames:
 
 class MambaMixer(Mixer):
     graph_safe = True
+    #: a step in which some request brings more rows than this runs the chunk-parallel kernels (bfloat16, a state of 64
+    #: or 128 entries a side per head); other steps walk each request's rows token by token from its state
+    CHUNKED_FROM = 8
 
     def __init__(self, hidden: int, heads: int, vdim: int, state: int, groups: int, taps: int, norm_groups: int, eps: float,
                  names: MambaNames):
@@ -89,12 +92,21 @@ class MambaMixer(Mixer):
     def forward(self, ctx, cache, x: torch.Tensor) -> torch.Tensor:
         rows = x.shape[0]
         proj = ops.linear(x, self.w_in, error_word=ctx.error_word)
-        xbc = torch.empty((rows, self.channels), dtype=torch.float32, device=x.device)
+        counts = [b - a for a, b in zip(ctx.host_cu_rows, ctx.host_cu_rows[1:])]
+        chunked = (len(counts) == ctx.num_requests and max(counts, default=0) > self.CHUNKED_FROM
+                   and ops.mamba_chunks_takes(proj.dtype, self.vdim, self.state))
+        xbc = torch.empty((rows, self.channels), dtype=proj.dtype if chunked else torch.float32, device=x.device)
         ops.mamba_conv(proj, self.conv, self.conv_bias, ctx.positions, ctx.row_request, ctx.cu_rows, ctx.state_slots,
                        cache.state, xbc, ctx.num_requests, read_only=not cache.writable, **self.sizes)
         y = torch.empty((rows, self.inner), dtype=torch.float32, device=x.device)
-        ops.mamba_scan(proj, xbc, self.a_log, self.d, self.dt_bias, ctx.positions, ctx.cu_rows, ctx.state_slots, cache.state, y,
-                       ctx.num_requests, read_only=not cache.writable, **self.sizes)
+        if chunked:
+            # prompt portions: chunks in parallel on the tensor cores
+            chunks = sum(-(-count // ops.MAMBA_CHUNK_TOKENS) for count in counts)
+            ops.mamba_chunks(proj, xbc, self.a_log, self.d, self.dt_bias, ctx.positions, ctx.cu_rows, ctx.state_slots,
+                             cache.state, y, ctx.num_requests, chunks, read_only=not cache.writable, **self.sizes)
+        else:
+            ops.mamba_scan(proj, xbc, self.a_log, self.d, self.dt_bias, ctx.positions, ctx.cu_rows, ctx.state_slots, cache.state,
+                           y, ctx.num_requests, read_only=not cache.writable, **self.sizes)
         gated = torch.empty((rows, self.inner), dtype=x.dtype, device=x.device)
         ops.mamba_gate_norm(y, proj, self.norm, self.eps, self.norm_groups, gated)
         return ops.linear(gated, self.w_o, error_word=ctx.error_word, partial_ok=True)

@@ -192,6 +192,87 @@ def test_state_space_mixer_over_states_in_slots(dtype, heads, vdim, nstate, grou
                     close(kept_inputs, last_inputs, torch.float32, f"second step, kept inputs of request {r}", 1e-6)
 
 
+@pytest.mark.parametrize("heads,vdim,nstate,groups,taps", [(8, 64, 64, 4, 4), (2, 64, 128, 1, 4), (4, 128, 64, 2, 3), (2, 128, 128, 2, 2)])
+def test_state_space_mixer_in_chunks_on_the_tensor_cores(heads, vdim, nstate, groups, taps):
+    """Prompt portions in bfloat16 run as chunks of 128 tokens in parallel: four requests in one step (a prompt of more
+    than two chunks from position 0 in a slot that holds rubbish, a one-token prompt, a later portion of one chunk and
+    one token from a given state, a portion of exactly one chunk), then a second step that continues them.  The
+    recurrence is checked against the plain one over the convolved inputs as the kernel rounded them, so what is left is
+    the error of the chunked arithmetic; the states go on into the token-by-token kernel."""
+    from sglang_rs_b200 import ops
+    dtype = torch.bfloat16
+    sizes = dict(heads=heads, vdim=vdim, nstate=nstate, groups=groups, taps=taps)
+    inner, channels = heads * vdim, heads * vdim + 2 * groups * nstate
+    counts, starts, slots = [300, 1, 129, 128], [0, 0, 70, 9], [2, 5, 0, 3]
+    counts2, slots2 = [2, 257, 1, 130], [2, 0, 3, 5]            # requests 0, 2, 3, 1 go on
+    order2 = [0, 2, 3, 1]
+    total, total2 = sum(counts), sum(counts2)
+    w, proj = mamba_inputs(heads, vdim, nstate, groups, taps, total + total2, nstate + taps, dtype)
+    state = torch.randn(6, ops.mamba_slot_floats(**sizes), device=DEV)
+    given = state.cpu().double()
+    weights = {k: v.to(DEV) for k, v in w.items()}
+
+    def unpack(slot_row):
+        return (slot_row[:(taps - 1) * channels].reshape(taps - 1, channels),
+                slot_row[(taps - 1) * channels:].reshape(heads, vdim, nstate).transpose(1, 2))
+
+    def run(rows, counts, starts, slots, chunked=True, read_only=False):
+        cu = np.cumsum([0] + counts).tolist()
+        positions = [s + i for s, c in zip(starts, counts) for i in range(c)]
+        row_request = [r for r, c in enumerate(counts) for _ in range(c)]
+        on = proj[rows].to(DEV, dtype)
+        xbc = torch.full((len(positions), channels), float("nan"), device=DEV, dtype=dtype if chunked else torch.float32)
+        ops.mamba_conv(on, weights["conv"], weights["conv.b"], dev(positions), dev(row_request), dev(cu), dev(slots), state, xbc,
+                       len(counts), read_only=read_only, **sizes)
+        y = torch.full((len(positions), inner), float("nan"), device=DEV)
+        if chunked:
+            chunks = sum(-(-c // ops.MAMBA_CHUNK_TOKENS) for c in counts)
+            ops.mamba_chunks(on, xbc, weights["A_log"], weights["D"], weights["dt_bias"], dev(positions), dev(cu), dev(slots), state,
+                             y, len(counts), chunks, read_only=read_only, **sizes)
+        else:
+            ops.mamba_scan(on, xbc, weights["A_log"], weights["D"], weights["dt_bias"], dev(positions), dev(cu), dev(slots), state, y,
+                           len(counts), read_only=read_only, **sizes)
+        return cu, xbc, y
+
+    def plain(rows, xbc, begin):
+        steps = pd.softplus(seen(proj[rows], dtype)[:, inner + channels:inner + channels + heads] + w["dt_bias"].double())
+        x = xbc.cpu().double()
+        T = x.shape[0]
+        y, last = pd.recurrence(x[:, :inner].reshape(T, heads, vdim), x[:, inner:inner + groups * nstate].reshape(T, groups, nstate),
+                                x[:, inner + groups * nstate:].reshape(T, groups, nstate), steps, w["A_log"].double(), w["D"].double(), begin)
+        return y.reshape(T, inner), last
+
+    cu, xbc, y = run(slice(0, total), counts, starts, slots)
+    after = {}
+    for r in range(4):
+        rows = slice(cu[r], cu[r + 1])
+        inputs, begin = unpack(given[slots[r]])
+        if starts[r] == 0:
+            inputs, begin = torch.zeros_like(inputs), torch.zeros_like(begin)
+        want_xbc, _, last_inputs, _ = plain_mixer_core(proj[rows], w, sizes, dtype, inputs, begin)
+        close(xbc[rows], want_xbc, dtype, f"convolved inputs of request {r}", 6e-3)
+        want_y, last = plain(rows, xbc[rows], begin)
+        after[r] = (last_inputs, last)
+        close(y[rows], want_y, torch.float32, f"request {r}", 1e-4)
+        kept_inputs, kept = unpack(state[slots[r]].cpu().double())
+        close(kept, last, torch.float32, f"state of request {r}", 1e-4)
+        close(kept_inputs, last_inputs, torch.float32, f"kept inputs of request {r}", 1e-6)
+    close(state[1], given[1], torch.float32, "a slot that no request holds", 0.0)
+    starts2 = [starts[r] + counts[r] for r in order2]
+    before = state.clone()
+    for chunked, read_only in ((True, True), (False, True), (True, False)):
+        cu2, xbc2, y2 = run(slice(total, total + total2), counts2, starts2, slots2, chunked=chunked, read_only=read_only)
+        if read_only:
+            assert torch.equal(state, before)
+        for i, r in enumerate(order2):
+            rows = slice(total + cu2[i], total + cu2[i + 1])
+            want_y, last = plain(rows, xbc2[cu2[i]:cu2[i + 1]], after[r][1])
+            close(y2[cu2[i]:cu2[i + 1]], want_y, torch.float32, f"second step, request {r}, chunked {chunked}", 1e-4)
+            if not read_only:
+                _, kept = unpack(state[slots2[i]].cpu().double())
+                close(kept, last, torch.float32, f"second step, state of request {r}", 1e-4)
+
+
 def test_state_space_mixer_keeps_a_token_through_a_slow_decay():
     """One head decays by 0.9995 a token: after 700 tokens, cut into three steps, the first token still makes up most of
     the result; the head beside it forgets within a few tokens."""
