@@ -10,13 +10,16 @@
 // A request's slot of state holds, in 32-bit floats, the last taps - 1 inputs of the convolution
 // [taps - 1][channels] (oldest first) followed by S as [heads][P][N] (a column's N entries together).  Kernels:
 //
-//   srb_mamba_conv        the convolution + SiLU of every row of the step (32-bit result), reading earlier rows of the
+//   srb_mamba_conv        the convolution + SiLU of every row of the step (32-bit result, or rounded to bfloat16 for the
+//                         chunk kernels), reading earlier rows of the
 //                         same request from the step and, before the step's first row, from the slot; then the slot's
 //                         inputs are replaced by the last taps - 1 of the sequence (a second launch: rows read the old ones)
 //   srb_mamba_scan        the recurrence, token by token: a block owns a head's N x PB slice of the state in registers
 //                         (PB columns, N cut over the lanes beside each column), stages 16 tokens' B, C, x, dt at a time in
 //                         shared memory and walks them; decoded tokens and prompt portions take the same arithmetic, so a
 //                         row's result does not depend on how the sequence was cut
+//   srb_mamba_chunks      the same recurrence for prompt portions in bfloat16, in chunks of 128 tokens that run in parallel
+//                         on the tensor cores (described above those kernels)
 //   srb_mamba_gate_norm   y * silu(z), RMS norm in `norm_groups` equal parts, times the weight, rounded
 //
 // Decays, step sizes, the state, the sums and the norm are 32-bit in both dtypes.  A request whose first row of the step
@@ -29,6 +32,7 @@ SRB_DEFINE_PDL_SWITCH()
 
 #define MAMBA_MAX_TAPS 16
 #define MAMBA_TOKENS 16        // tokens staged in shared memory at a time
+#define MAMBA_CONV_ROWS 8      // rows of the step that one thread of the convolution takes
 #define MAMBA_THREADS 256
 
 struct MambaShape {
@@ -42,33 +46,110 @@ struct MambaShape {
 __device__ __forceinline__ float mamba_silu(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float mamba_softplus(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-template <typename T, typename O>
+// SiLU of the convolution's sum as the result's type: a bfloat16 result keeps 8 bits of mantissa, so the quick exponential
+// and quotient (about 22 bits) round to the same number but for ties
+template <typename O> __device__ __forceinline__ O mamba_conv_result(float acc);
+template <> __device__ __forceinline__ float mamba_conv_result<float>(float acc) { return mamba_silu(acc); }
+template <> __device__ __forceinline__ __nv_bfloat16 mamba_conv_result<__nv_bfloat16>(float acc) {
+  return __float2bfloat16_rn(__fdividef(acc, 1.0f + __expf(-acc)));
+}
+
+// grid (channel blocks, ceil(rows / ROWS)), so that blocks that run together read neighbouring pieces of the same rows:
+// a thread takes one channel of ROWS consecutive rows (MAMBA_CONV_ROWS in steps
+// of many rows, so that the filter is read once and the rows' loads are in flight together; 1 in steps of few rows).
+// TAPS: the filter's length, or 0 for any.
+template <typename T, typename O, int TAPS, int ROWS>
 __global__ void mamba_conv_kernel(const T* __restrict__ proj, const float* __restrict__ weight, const float* __restrict__ bias,
                                   const int* __restrict__ positions, const int* __restrict__ row_request,
                                   const int* __restrict__ cu_rows, const int* __restrict__ state_slots,
-                                  const float* __restrict__ state, O* __restrict__ out, MambaShape s) {
+                                  const float* __restrict__ state, O* __restrict__ out, int rows, MambaShape s) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
-  const int row = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= s.channels) return;
-  const int pos = positions[row];
-  O* dst = out + (size_t)row * s.channels + c;
-  if (pos < 0) { *dst = srb_from_float<O>(0.f); return; }
-  const int request = row_request[row];
-  const int ahead = row - cu_rows[request];            // rows of this request before this one in the step
-  const float* kept = state + (size_t)state_slots[request] * s.slot_floats;
-  float acc = bias[c];
-  for (int j = 0; j < s.taps; ++j) {
-    const int back = s.taps - 1 - j;
-    if (pos - back < 0) continue;                      // zeros before the start of the sequence
-    float u;
-    if (back <= ahead)
-      u = srb_to_float(proj[(size_t)(row - back) * s.proj_pitch + s.inner + c]);
-    else
-      u = kept[(size_t)(s.taps - 1 - (back - ahead)) * s.channels + c];
-    acc = fmaf(weight[(size_t)c * s.taps + j], u, acc);
+  const int taps = TAPS > 0 ? TAPS : s.taps;
+  constexpr int HELD = TAPS > 0 ? TAPS : 1;
+  float w[HELD];
+  if (TAPS > 0) {
+#pragma unroll
+    for (int j = 0; j < HELD; ++j) w[j] = weight[(size_t)c * TAPS + j];
   }
-  *dst = srb_from_float<O>(mamba_silu(acc));
+  const float b = bias[c];
+  const int row0 = blockIdx.y * ROWS;
+  // what the rows need to know, all loads in flight together: position, rows of the request before it, the slot
+  int pos[ROWS], ahead[ROWS], slot[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const bool live = row0 + r < rows;
+    pos[r] = live ? positions[row0 + r] : -1;
+    ahead[r] = live ? row_request[row0 + r] : 0;
+  }
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int request = ahead[r];
+    ahead[r] = row0 + r - cu_rows[request];
+    slot[r] = state_slots[request];
+  }
+  if constexpr (TAPS > 0) {
+    // the inputs of rows row0 - (TAPS - 1) .. row0 + ROWS - 1 of the step, whichever request they belong to
+    float u[ROWS + HELD - 1];
+#pragma unroll
+    for (int k = 0; k < ROWS + HELD - 1; ++k) {
+      const int row = row0 + k - (HELD - 1);
+      u[k] = (row >= 0 && row < rows) ? srb_to_float(proj[(size_t)row * s.proj_pitch + s.inner + c]) : 0.f;
+    }
+    // rows in the middle of a request's rows of the step: every input is one of the step's
+    bool inside = row0 + ROWS <= rows;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) inside = inside && pos[r] >= HELD - 1 && ahead[r] >= HELD - 1;
+    if (inside) {
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        float acc = b;
+#pragma unroll
+        for (int j = 0; j < HELD; ++j) acc = fmaf(w[j], u[r + j], acc);
+        out[(size_t)(row0 + r) * s.channels + c] = mamba_conv_result<O>(acc);
+      }
+      return;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (row0 + r >= rows) break;
+      O* dst = out + (size_t)(row0 + r) * s.channels + c;
+      if (pos[r] < 0) { *dst = srb_from_float<O>(0.f); continue; }
+      const float* kept = state + (size_t)slot[r] * s.slot_floats;
+      float acc = b;
+#pragma unroll
+      for (int j = 0; j < HELD; ++j) {
+        const int back = HELD - 1 - j;
+        if (pos[r] - back < 0) continue;                   // zeros before the start of the sequence
+        const float v = back <= ahead[r] ? u[r + j] : kept[(size_t)(HELD - 1 - (back - ahead[r])) * s.channels + c];
+        acc = fmaf(w[j], v, acc);
+      }
+      *dst = mamba_conv_result<O>(acc);
+    }
+  } else {
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int row = row0 + r;
+    if (row >= rows) break;
+    O* dst = out + (size_t)row * s.channels + c;
+    if (pos[r] < 0) { *dst = srb_from_float<O>(0.f); continue; }
+    const float* kept = state + (size_t)slot[r] * s.slot_floats;
+    float acc = b;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;
+      if (pos[r] - back < 0) continue;                     // zeros before the start of the sequence
+      float v;
+      if (back <= ahead[r])
+        v = srb_to_float(proj[(size_t)(row - back) * s.proj_pitch + s.inner + c]);
+      else
+        v = kept[(size_t)(taps - 1 - (back - ahead[r])) * s.channels + c];
+      acc = fmaf(weight[(size_t)c * taps + j], v, acc);
+    }
+    *dst = mamba_conv_result<O>(acc);
+  }
+  }
 }
 
 // One thread per (request, channel): the slot's inputs become the last taps - 1 of the sequence after this step.
@@ -183,7 +264,7 @@ mamba_scan_kernel(const T* __restrict__ proj, const float* __restrict__ xbc, con
   }
 }
 
-// grid (rows, norm groups): out = rms_part(y * silu(z)) * weight
+// grid (rows * norm groups), a row's parts in neighbouring blocks: out = rms_part(y * silu(z)) * weight
 template <typename T>
 __global__ void mamba_gate_norm_kernel(const float* __restrict__ y, const T* __restrict__ proj, long long proj_pitch,
                                        const float* __restrict__ weight, float eps, int inner, int part,
@@ -192,7 +273,7 @@ __global__ void mamba_gate_norm_kernel(const float* __restrict__ y, const T* __r
   float* scratch = gate_smem + part;
   srb_launch_dependents();
   srb_grid_dependency_wait();
-  const int row = blockIdx.x, base = blockIdx.y * part;
+  const int parts = inner / part, row = blockIdx.x / parts, base = (blockIdx.x % parts) * part;
   float partial = 0.f;
   for (int i = threadIdx.x; i < part; i += blockDim.x) {
     const float z = srb_to_float(proj[(size_t)row * proj_pitch + base + i]);
@@ -203,6 +284,47 @@ __global__ void mamba_gate_norm_kernel(const float* __restrict__ y, const T* __r
   const float inv = 1.0f / sqrtf(srb_block_sum(partial, scratch) / (float)part + eps);
   for (int i = threadIdx.x; i < part; i += blockDim.x)
     out[(size_t)row * inner + base + i] = srb_from_float<T>(gate_smem[i] * inv * weight[base + i]);
+}
+
+__device__ __forceinline__ float4 mamba_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 mamba_load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void mamba_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void mamba_store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const unsigned*>(&a);
+  raw.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same with four consecutive entries a thread (parts, rows and pointers on 16-byte borders of floats).
+template <typename T>
+__global__ void mamba_gate_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ proj, long long proj_pitch,
+                                           const float* __restrict__ weight, float eps, int inner, int part,
+                                           T* __restrict__ out) {
+  extern __shared__ __align__(16) float gate_vec_smem[];    // part floats, then 33 of scratch
+  float* scratch = gate_vec_smem + part;
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int parts = inner / part, row = blockIdx.x / parts, base = (blockIdx.x % parts) * part;
+  float partial = 0.f;
+  for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
+    const float4 z = mamba_load4(proj + (size_t)row * proj_pitch + base + i);
+    float4 v = mamba_load4(y + (size_t)row * inner + base + i);
+    v.x *= mamba_silu(z.x); v.y *= mamba_silu(z.y); v.z *= mamba_silu(z.z); v.w *= mamba_silu(z.w);
+    *reinterpret_cast<float4*>(gate_vec_smem + i) = v;
+    partial += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  const float inv = 1.0f / sqrtf(srb_block_sum(partial, scratch) / (float)part + eps);
+  for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(gate_vec_smem + i), w = mamba_load4(weight + base + i);
+    mamba_store4(out + (size_t)row * inner + base + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+  }
 }
 
 static int mamba_shape(MambaShape& s, int heads, int vdim, int nstate, int groups, int taps, long long proj_pitch,
@@ -228,9 +350,21 @@ static int launch_mamba_conv(const void* proj, const float* weight, const float*
                              const int* row_request, const int* cu_rows, const int* state_slots, float* state, void* out,
                              int rows, int requests, int write_state, const MambaShape& s, cudaStream_t st) {
   const int block = 128;
-  const dim3 grid(rows, (s.channels + block - 1) / block), keep_grid((s.channels + block - 1) / block, requests);
-  SRB_CUDA_CALL(srb_launch(mamba_conv_kernel<T, O>, grid, dim3(block), 0, st, (const T*)proj, weight, bias, positions,
-                           row_request, cu_rows, state_slots, (const float*)state, (O*)out, s));
+  const bool many = rows >= 64 * MAMBA_CONV_ROWS;
+  const int per = many ? MAMBA_CONV_ROWS : 1;
+  const dim3 grid((s.channels + block - 1) / block, (rows + per - 1) / per);
+  if (grid.y > 65535) SRB_FAIL("mamba_conv: %d rows exceed one launch", rows);
+  const dim3 keep_grid((s.channels + block - 1) / block, requests);
+#define MAMBA_CONV_LAUNCH(TAPS, ROWS)                                                                                        \
+  SRB_CUDA_CALL(srb_launch(mamba_conv_kernel<T, O, TAPS, ROWS>, grid, dim3(block), 0, st, (const T*)proj, weight, bias,     \
+                           positions, row_request, cu_rows, state_slots, (const float*)state, (O*)out, rows, s))
+  if (s.taps == 4 && many) MAMBA_CONV_LAUNCH(4, MAMBA_CONV_ROWS);
+  else if (s.taps == 4) MAMBA_CONV_LAUNCH(4, 1);
+  else if (s.taps == 3 && many) MAMBA_CONV_LAUNCH(3, MAMBA_CONV_ROWS);
+  else if (s.taps == 2 && many) MAMBA_CONV_LAUNCH(2, MAMBA_CONV_ROWS);
+  else if (many) MAMBA_CONV_LAUNCH(0, MAMBA_CONV_ROWS);
+  else MAMBA_CONV_LAUNCH(0, 1);
+#undef MAMBA_CONV_LAUNCH
   if (write_state && s.taps > 1)
     SRB_CUDA_CALL(srb_launch(mamba_conv_keep_kernel<T>, keep_grid, dim3(block), 0, st, (const T*)proj, positions, cu_rows,
                              state_slots, state, s));
@@ -304,19 +438,36 @@ extern "C" int srb_mamba_gate_norm(const float* y, const void* proj, long long p
   if (rows <= 0) return SRB_OK;
   if (inner <= 0 || norm_groups <= 0 || inner % norm_groups) SRB_FAIL("mamba_gate_norm: %d entries do not split into %d equal parts", inner, norm_groups);
   if (!(eps >= 0.f)) SRB_FAIL("mamba_gate_norm: eps must be finite and non-negative");
-  if (norm_groups > 65535) SRB_FAIL("mamba_gate_norm: %d parts exceed one launch", norm_groups);
+  if ((long long)rows * norm_groups > 0x7fffffffLL) SRB_FAIL("mamba_gate_norm: %d rows of %d parts exceed one launch", rows, norm_groups);
   const int part = inner / norm_groups;
   const size_t smem = (size_t)(part + 33) * sizeof(float);
   if (smem > 227 * 1024) SRB_FAIL("mamba_gate_norm: a part of %d entries needs %zu bytes of shared memory (limit 232448)", part, smem);
-  const int block = part >= 2048 ? 512 : (part >= 512 ? 256 : 128);
   cudaStream_t st = (cudaStream_t)stream;
+  const bool vec = part % 4 == 0 && proj_pitch % 4 == 0 && !(((uintptr_t)y | (uintptr_t)proj | (uintptr_t)weight | (uintptr_t)out) & 15);
+  if (vec) {
+    const int vblock = part >= 2048 ? 256 : (part >= 512 ? 128 : 64);
+    if (dtype == SRB_DTYPE_F32) {
+      if (smem > 48 * 1024) SRB_CUDA_CALL(cudaFuncSetAttribute(mamba_gate_norm_vec_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      SRB_CUDA_CALL(srb_launch(mamba_gate_norm_vec_kernel<float>, dim3((unsigned)rows * norm_groups), dim3(vblock), smem, st, y, (const float*)proj,
+                               proj_pitch, weight, eps, inner, part, (float*)out));
+    } else if (dtype == SRB_DTYPE_BF16) {
+      if (smem > 48 * 1024) SRB_CUDA_CALL(cudaFuncSetAttribute(mamba_gate_norm_vec_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      SRB_CUDA_CALL(srb_launch(mamba_gate_norm_vec_kernel<__nv_bfloat16>, dim3((unsigned)rows * norm_groups), dim3(vblock), smem, st, y,
+                               (const __nv_bfloat16*)proj, proj_pitch, weight, eps, inner, part, (__nv_bfloat16*)out));
+    } else {
+      SRB_FAIL("mamba_gate_norm: unknown dtype %d", dtype);
+    }
+    SRB_LAUNCH_CHECK("mamba_gate_norm");
+    return SRB_OK;
+  }
+  const int block = part >= 2048 ? 512 : (part >= 512 ? 256 : 128);
   if (dtype == SRB_DTYPE_F32) {
     if (smem > 48 * 1024) SRB_CUDA_CALL(cudaFuncSetAttribute(mamba_gate_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SRB_CUDA_CALL(srb_launch(mamba_gate_norm_kernel<float>, dim3(rows, norm_groups), dim3(block), smem, st, y, (const float*)proj,
+    SRB_CUDA_CALL(srb_launch(mamba_gate_norm_kernel<float>, dim3((unsigned)rows * norm_groups), dim3(block), smem, st, y, (const float*)proj,
                              proj_pitch, weight, eps, inner, part, (float*)out));
   } else if (dtype == SRB_DTYPE_BF16) {
     if (smem > 48 * 1024) SRB_CUDA_CALL(cudaFuncSetAttribute(mamba_gate_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SRB_CUDA_CALL(srb_launch(mamba_gate_norm_kernel<__nv_bfloat16>, dim3(rows, norm_groups), dim3(block), smem, st, y,
+    SRB_CUDA_CALL(srb_launch(mamba_gate_norm_kernel<__nv_bfloat16>, dim3((unsigned)rows * norm_groups), dim3(block), smem, st, y,
                              (const __nv_bfloat16*)proj, proj_pitch, weight, eps, inner, part, (__nv_bfloat16*)out));
   } else {
     SRB_FAIL("mamba_gate_norm: unknown dtype %d", dtype);
