@@ -162,7 +162,8 @@ MARK = 41          # the token that the made-up models below look for
 FILL = 40          # what stands where the mark would be, in sequences without it
 
 
-def marked_folder(tmp_path, dtype: torch.dtype, mixer: str, window: Optional[int] = None, shared: bool = False) -> str:
+def marked_folder(tmp_path, dtype: torch.dtype, mixer: str, window: Optional[int] = None, shared: bool = False,
+                  wide: bool = False) -> str:
     """One or two layers that look for the one position holding ``MARK``.
 
     Only that token's embedding has an entry in channel 0; channel 1 is the same constant in every embedding.
@@ -170,16 +171,18 @@ def marked_folder(tmp_path, dtype: torch.dtype, mixer: str, window: Optional[int
     so the mark's score stands far above all others wherever it is visible.  With ``shared`` a second attention layer
     reads the first one's latents through a window twice as wide and looks for the mark in the same way.
     ``mamba``: head 0 decays by about 0.999 a token; its B and x read channel 0 (through the filter's current tap), its C
-    reads the constant, so the state keeps the mark for hundreds of tokens and every later result holds it."""
+    reads the constant, so the state keeps the mark for hundreds of tokens and every later result holds it.  ``wide``:
+    heads of 64 columns over states of 64 entries, the sizes at which prompt portions in bfloat16 run in parallel chunks."""
     from sglang_rs_b200.weights import read_model_dir, write_file
     if mixer == "attention":
         layers = [layer(attention(2, 16, 8, 16, window=window, scale=0.25), moe(3, 1, 8))]
         if shared:
             layers.append(layer(attention(3, 8, 8, 16, window=2 * window, kv_from=0, scale=0.35), None))
     else:
-        layers = [layer(state_space(2, 8, 8, 1, 3, 1), moe(3, 1, 8))]
+        P, N = (64, 64) if wide else (8, 8)
+        layers = [layer(state_space(2, P, N, 1, 3, 1), moe(3, 1, 8))]
     doc = config(32, 60, layers, groups=1, mult=1.0, logit_scale=1.0)
-    folder = make_folder(tmp_path, f"marked_{mixer}_{window}_{shared}", doc, seed=7, dtype=dtype)
+    folder = make_folder(tmp_path, f"marked_{mixer}_{window}_{shared}_{wide}", doc, seed=7, dtype=dtype)
     t = {k: v.float().clone() for k, v in read_model_dir(folder).items()}
     t["embed"][:, 0] = 0
     t["embed"][MARK, 0] = 6.0
@@ -202,24 +205,24 @@ def marked_folder(tmp_path, dtype: torch.dtype, mixer: str, window: Optional[int
             t[p + "uv"][:8, 0] = 3.0
             t[p + "o"][:, :8] *= 10.0
     else:
-        inner, N = 16, 8
+        inner = 2 * P
         w = t["l0.mix.in"]
-        w[inner:inner + 8] = 0                                    # head 0's x
-        w[inner:inner + 8, 0] = 1.0
+        w[inner:inner + P] = 0                                    # head 0's x
+        w[inner:inner + P, 0] = 1.0
         w[2 * inner:2 * inner + N] = 0                            # B
         w[2 * inner:2 * inner + N, 0] = 1.0
         w[2 * inner + N:2 * inner + 2 * N] = 0                    # C
         w[2 * inner + N:2 * inner + 2 * N, 1] = 1.0
         w[2 * inner + 2 * N] = 0                                  # head 0's step size: softplus(0) everywhere
         conv, bias = t["l0.mix.conv"], t["l0.mix.conv.b"]
-        for rows in (slice(0, 8), slice(inner, inner + 2 * N)):
+        for rows in (slice(0, P), slice(inner, inner + 2 * N)):
             conv[rows] = 0
             conv[rows, -1] = 1.0
             bias[rows] = 0
         t["l0.mix.A_log"][0], t["l0.mix.dt_bias"][0], t["l0.mix.D"][0] = -6.5, 0.0, 0.0
         t["l0.mix.A_log"][1], t["l0.mix.dt_bias"][1] = 0.5, 0.0
         t["l0.mix.norm"][:] = 1.0
-        t["l0.mix.o"][:, :8] *= 10.0
+        t["l0.mix.o"][:, :P] *= 10.0
     write_file(os.path.join(folder, "model.safetensors"), {k: v.to(dtype) for k, v in t.items()})
     return folder
 

@@ -543,10 +543,12 @@ def test_a_key_at_the_edge_of_a_window_decides_the_logits(tmp_path, dtype_name, 
 
 
 @pytest.mark.parametrize("dtype_name,stored,tolerance", DTYPES)
-def test_a_state_keeps_a_token_from_hundreds_of_positions_back(tmp_path, dtype_name, stored, tolerance):
+@pytest.mark.parametrize("wide", [False, True])
+def test_a_state_keeps_a_token_from_hundreds_of_positions_back(tmp_path, dtype_name, stored, tolerance, wide):
     """The mark at position 3 of 420 tokens, in a model whose state-space head decays by 0.999 a token: the last logits
-    hang on it.  A state that is lost between steps, zeroed with a slot or mixed up in a batch shows."""
-    folder = dh.marked_folder(tmp_path, stored, "mamba")
+    hang on it.  A state that is lost between steps, zeroed with a slot or mixed up in a batch shows.  ``wide``: at the
+    sizes whose prompt portions in bfloat16 run as parallel chunks, so a chunk's state that does not reach the next shows."""
+    folder = dh.marked_folder(tmp_path, stored, "mamba", wide=wide)
     doc, tensors = dh.load_folder(folder)
     tokens = _with_mark(doc, 420, 3, seed=1)
     other = _with_mark(doc, 90, 50, seed=2)
