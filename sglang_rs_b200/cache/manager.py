@@ -152,7 +152,7 @@ class PagedLayerCache:
     """What a mixer with a :class:`PagedKV` need is handed for one layer call."""
     group: GroupKey
     k_pool: Optional[torch.Tensor]      # [pages, kv_heads, page_size, head_dim]
-    v_pool: Optional[torch.Tensor]      # None for a need without values: the key rows are all that is kept
+    v_pool: Optional[torch.Tensor]      # [pages, kv_heads, page_size, value width]; None for a need without values: the key rows are all that is kept
     writable: bool = True
 
     def read_only(self) -> "PagedLayerCache":
@@ -252,7 +252,7 @@ class CacheManager:
                     # one page more than the allocator owns: rows that pad a captured step write there
                     shape = (self.allocators[key].num_pages + 1, need.num_kv_heads, self.page_size, need.head_dim)
                     pools = (torch.zeros(shape, dtype=dtype, device=device),
-                             torch.zeros(shape, dtype=dtype, device=device) if need.values else None)
+                             torch.zeros((*shape[:3], need.value_width), dtype=dtype, device=device) if need.values else None)
                 self.layer_caches.append(PagedLayerCache(key, *pools))
             elif isinstance(need, RequestState):
                 state = None

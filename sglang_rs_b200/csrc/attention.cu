@@ -41,3 +41,15 @@ extern "C" int srb_paged_attention_masked(const void* q, const void* k_pool, con
                                          table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, chunk,
                                          split_size, max_splits, scale, error_word, dtype, sinks, value_dim, stream);
 }
+
+// The same with a gate per (row, query head): `gates` (float [rows, n_q], or null) multiplies each head's result.
+extern "C" int srb_paged_attention_gated(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                         float* part_acc, float* part_ml, const int* positions,
+                                         const int* row_request, const int* block_table, int table_stride, int rows,
+                                         int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                         int chunk, int split_size, int max_splits, float scale, int* error_word,
+                                         int dtype, const float* sinks, int value_dim, const float* gates, void* stream) {
+  return paged_attention_dispatch_masked(q, k_pool, v_pool, out, part_acc, part_ml, positions, row_request, block_table,
+                                         table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, chunk,
+                                         split_size, max_splits, scale, error_word, dtype, sinks, value_dim, stream, gates);
+}

@@ -15,7 +15,9 @@
 //  * a sink: `sinks` holds one float per query head; exp(sink_h) is added to the softmax's denominator and to nothing
 //    else.  It belongs to no key, gets no share of the values, is taken as it is (the score scale does not apply), and is
 //    added exactly one time per row, also when the row's keys are split over several blocks (the merge adds it);
-//  * values narrower than keys: the output and the value rows are `value_dim` wide.  With
+//  * a gate: `gates` holds one float per (row, query head) that multiplies the head's result (a mixer's output gate,
+//    already passed through its sigmoid), applied where the result is normalised and written;
+//  * values of another width than the keys: the output and the value rows are `value_dim` wide.  With
 //    `shared_values` the value of a key is the first `value_dim` entries of its key row (a cache that
 //    keeps one latent row per token serves as key and as value), and v_pool is not read.
 //
@@ -50,6 +52,7 @@ struct AttnParams {
   int shared_values;         // 1: values are the first value_dim entries of the key rows
   int head_chunks;           // blocks per (row, kv head, split) along the query heads
   int heads_per_block;
+  const float* gates = nullptr;   // [rows, n_q] or null: a factor on the result of every (row, query head)
 };
 
 // The first key that a row at `pos` may see: the start of its window, or of its chunk of positions, whichever is later.
@@ -183,7 +186,7 @@ __global__ void paged_attention_kernel(const T* __restrict__ q, const T* __restr
 #pragma unroll
       for (int j = 0; j < DIM_PER_LANE; ++j) acc[j] *= correction;
     }
-    const float inv = 1.0f / l;
+    const float inv = p.gates ? p.gates[(size_t)row * p.n_q + q_head] / l : 1.0f / l;
 #pragma unroll
     for (int j = 0; j < DIM_PER_LANE; ++j) {
       const int e = lane + 32 * j;
@@ -221,7 +224,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc, con
   for (int s = 0; s < count; ++s) m = fmaxf(m, part_ml[(first + s) * 2]);
   float l = p.sinks ? expf(p.sinks[q_head] - m) : 0.f;   // the sink counts once, whatever the number of splits
   for (int s = 0; s < count; ++s) l += part_ml[(first + s) * 2 + 1] * expf(part_ml[(first + s) * 2] - m);
-  const float inv = 1.0f / l;
+  const float inv = p.gates ? p.gates[(size_t)row * p.n_q + q_head] / l : 1.0f / l;
   for (int e = threadIdx.x; e < p.value_dim; e += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < count; ++s)
@@ -262,16 +265,17 @@ static int paged_attention_dispatch_masked(const void* q, const void* k_pool, co
                                            const int* row_request, const int* block_table, int table_stride, int rows,
                                            int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
                                            int chunk, int split_size, int max_splits, float scale, int* error_word,
-                                           int dtype, const float* sinks, int value_dim, void* stream) {
+                                           int dtype, const float* sinks, int value_dim, void* stream,
+                                           const float* gates = nullptr) {
   if (rows <= 0) return SRB_OK;
   if (chunk < 0) SRB_FAIL("paged_attention: the chunk size must be non-negative");
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0)
     SRB_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
   if (head_dim <= 0) SRB_FAIL("paged_attention: head_dim %d must be positive", head_dim);
   if (value_dim == 0) value_dim = head_dim;
-  if (value_dim < 0 || value_dim > head_dim || value_dim > 1024)
-    SRB_FAIL("paged_attention: values of %d entries must be positive, at most as wide as the keys (%d) and at most 1024",
-             value_dim, head_dim);
+  if (value_dim < 0 || value_dim > 1024 || (!v_pool && value_dim > head_dim))
+    SRB_FAIL("paged_attention: values of %d entries must be positive, at most 1024 and, if they are the head of the key "
+             "rows (%d entries), no wider than those", value_dim, head_dim);
   if (page_size <= 0 || num_pages <= 0 || table_stride <= 0)
     SRB_FAIL("paged_attention: page size, page count and table stride must be positive");
   if (window < 0 || split_size < 0) SRB_FAIL("paged_attention: window and split size must be non-negative");
@@ -286,7 +290,7 @@ static int paged_attention_dispatch_masked(const void* q, const void* k_pool, co
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
   p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.split_size = split_size;
   p.max_splits = split_size == 0 ? 1 : max_splits; p.scale = scale; p.error_word = error_word;
-  p.sinks = sinks; p.value_dim = value_dim; p.shared_values = v_pool == nullptr;
+  p.sinks = sinks; p.value_dim = value_dim; p.shared_values = v_pool == nullptr; p.gates = gates;
   const int groups = n_q / n_kv;
   p.head_chunks = (groups + 31) / 32;
   p.heads_per_block = (groups + p.head_chunks - 1) / p.head_chunks;

@@ -347,7 +347,8 @@ template <typename T>
 __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                      const float* __restrict__ delta_f32, NormSpec inner, NormSpec outer,
                                      T* __restrict__ out, size_t out_pitch, const float* __restrict__ extra,
-                                     const int* __restrict__ row_index, int width, int write_residual) {
+                                     const int* __restrict__ row_index, int width, int write_residual,
+                                     const float* __restrict__ addend) {
   extern __shared__ float staged[];          // width floats, then 33 floats of scratch
   float* scratch = staged + width;
   srb_launch_dependents();
@@ -364,7 +365,8 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float x = residual[src + i];
     if (pending) x += staged[i];
-    if (write_residual && pending) residual[src + i] = x;
+    if (addend) x += addend[src + i];
+    if (write_residual && (pending || addend)) residual[src + i] = x;
     staged[i] = x;
   }
   if (!out) return;
@@ -376,13 +378,14 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
     for (int i = threadIdx.x; i < width; i += blockDim.x) dst[width + i] = srb_from_float<T>(extra[src + i]);
 }
 
-// `*_groups` (RMS norms only; 1: the whole row) and `*_scale` (1: none) as NormSpec says
-extern "C" int srb_norm_add_norm_ex(float* residual, const void* delta, const float* delta_f32, int inner_kind,
+// `*_groups` (RMS norms only; 1: the whole row) and `*_scale` (1: none) as NormSpec says.  `addend` (optional, float,
+// shaped like the residual): a second term of the sum, added after the pending one: x = residual + inner(delta) + addend.
+extern "C" int srb_norm_add_norm_plus(float* residual, const void* delta, const float* delta_f32, int inner_kind,
                                     const float* inner_weight, const float* inner_bias, float inner_eps, int inner_groups,
                                     float inner_scale, int outer_kind, const float* outer_weight, const float* outer_bias,
                                     float outer_eps, int outer_groups, float outer_scale, void* out, long long out_pitch,
                                     const float* extra, const int* row_index, int rows, int width, int write_residual,
-                                    int dtype, void* stream) {
+                                    int dtype, const float* addend, void* stream) {
   if (rows <= 0) return SRB_OK;
   for (int groups : {inner_groups, outer_groups})
     if (groups < 1 || width % groups) SRB_FAIL("norm_add_norm: a row of %d entries does not split into %d equal parts", width, groups);
@@ -406,19 +409,30 @@ extern "C" int srb_norm_add_norm_ex(float* residual, const void* delta, const fl
       SRB_CUDA_CALL(cudaFuncSetAttribute(norm_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SRB_CUDA_CALL(srb_launch(norm_add_norm_kernel<float>, dim3(rows), dim3(block), smem, s, residual, (const float*)delta,
                              delta_f32, inner, outer, (float*)out, (size_t)out_pitch, extra, row_index, width,
-                             write_residual));
+                             write_residual, addend));
   } else if (dtype == SRB_DTYPE_BF16) {
     if (smem > 48 * 1024)
       SRB_CUDA_CALL(cudaFuncSetAttribute(norm_add_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
     SRB_CUDA_CALL(srb_launch(norm_add_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(block), smem, s, residual,
                              (const __nv_bfloat16*)delta, delta_f32, inner, outer, (__nv_bfloat16*)out, (size_t)out_pitch,
-                             extra, row_index, width, write_residual));
+                             extra, row_index, width, write_residual, addend));
   } else {
     SRB_FAIL("norm_add_norm: unknown dtype %d", dtype);
   }
   SRB_LAUNCH_CHECK("norm_add_norm");
   return SRB_OK;
+}
+
+extern "C" int srb_norm_add_norm_ex(float* residual, const void* delta, const float* delta_f32, int inner_kind,
+                                    const float* inner_weight, const float* inner_bias, float inner_eps, int inner_groups,
+                                    float inner_scale, int outer_kind, const float* outer_weight, const float* outer_bias,
+                                    float outer_eps, int outer_groups, float outer_scale, void* out, long long out_pitch,
+                                    const float* extra, const int* row_index, int rows, int width, int write_residual,
+                                    int dtype, void* stream) {
+  return srb_norm_add_norm_plus(residual, delta, delta_f32, inner_kind, inner_weight, inner_bias, inner_eps, inner_groups,
+                                inner_scale, outer_kind, outer_weight, outer_bias, outer_eps, outer_groups, outer_scale, out,
+                                out_pitch, extra, row_index, rows, width, write_residual, dtype, nullptr, stream);
 }
 
 extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float* delta_f32, int inner_kind,

@@ -24,7 +24,8 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, size_t pitch, 
                                       const float* __restrict__ q_weight, const float* __restrict__ kv_weight,
                                       float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                       int rotary_dim, T* __restrict__ q_latent, T* __restrict__ pool,
-                                      const int* __restrict__ slots, long long pool_rows, int* error_word) {
+                                      const int* __restrict__ slots, long long pool_rows, int* error_word,
+                                      int interleaved, float magnitude) {
   __shared__ float scratch[33];
   srb_launch_dependents();
   srb_grid_dependency_wait();
@@ -64,19 +65,24 @@ __global__ void latent_prepare_kernel(const T* __restrict__ proj, size_t pitch, 
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float sine, cosine;
     sincosf(position * inv_freq[i], &sine, &cosine);
-    const float u = srb_to_float(shared_key[i]), v = srb_to_float(shared_key[i + half]);
-    dst[kv_rank + i] = srb_from_float<T>(u * cosine - v * sine);
-    dst[kv_rank + i + half] = srb_from_float<T>(v * cosine + u * sine);
+    sine *= magnitude; cosine *= magnitude;
+    const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+    const float u = srb_to_float(shared_key[ia]), v = srb_to_float(shared_key[ib]);
+    dst[kv_rank + ia] = srb_from_float<T>(u * cosine - v * sine);
+    dst[kv_rank + ib] = srb_from_float<T>(v * cosine + u * sine);
   }
   for (int i = rotary_dim + threadIdx.x; i < rot_dim; i += blockDim.x) dst[kv_rank + i] = shared_key[i];
 }
 
 // proj: [rows, pitch] with the query latent in columns [0, q_rank), the key/value latent behind it and the
 // shared key part behind that.  pool: [pool_rows, kv_rank + rot_dim]; slots null: nothing is stored.
-extern "C" int srb_latent_prepare(const void* proj, long long pitch, int rows, int q_rank, int kv_rank, int rot_dim,
-                                  const float* q_weight, const float* kv_weight, float eps, const int* positions,
-                                  const float* inv_freq, int rotary_dim, void* q_latent, void* pool, const int* slots,
-                                  long long pool_rows, int* error_word, int dtype, void* stream) {
+// `interleaved`: the rotation pairs entry 2i with entry 2i + 1 instead of i with i + dims/2; `magnitude` multiplies
+// every cosine and sine.
+extern "C" int srb_latent_prepare_ex(const void* proj, long long pitch, int rows, int q_rank, int kv_rank, int rot_dim,
+                                     const float* q_weight, const float* kv_weight, float eps, const int* positions,
+                                     const float* inv_freq, int rotary_dim, void* q_latent, void* pool, const int* slots,
+                                     long long pool_rows, int* error_word, int dtype, int interleaved, float magnitude,
+                                     void* stream) {
   if (rows <= 0) return SRB_OK;
   if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0) SRB_FAIL("latent_prepare: sizes %d, %d, %d do not describe latents", q_rank, kv_rank, rot_dim);
   if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > rot_dim)
@@ -88,16 +94,24 @@ extern "C" int srb_latent_prepare(const void* proj, long long pitch, int rows, i
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(latent_prepare_kernel<float>, dim3(rows), dim3(128), 0, s, (const float*)proj, (size_t)pitch,
                              q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, positions, inv_freq, rotary_dim,
-                             (float*)q_latent, (float*)pool, slots, pool_rows, error_word));
+                             (float*)q_latent, (float*)pool, slots, pool_rows, error_word, interleaved, magnitude));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s,
                              (const __nv_bfloat16*)proj, (size_t)pitch, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps,
                              positions, inv_freq, rotary_dim, (__nv_bfloat16*)q_latent, (__nv_bfloat16*)pool, slots,
-                             pool_rows, error_word));
+                             pool_rows, error_word, interleaved, magnitude));
   else
     SRB_FAIL("latent_prepare: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("latent_prepare");
   return SRB_OK;
+}
+
+extern "C" int srb_latent_prepare(const void* proj, long long pitch, int rows, int q_rank, int kv_rank, int rot_dim,
+                                  const float* q_weight, const float* kv_weight, float eps, const int* positions,
+                                  const float* inv_freq, int rotary_dim, void* q_latent, void* pool, const int* slots,
+                                  long long pool_rows, int* error_word, int dtype, void* stream) {
+  return srb_latent_prepare_ex(proj, pitch, rows, q_rank, kv_rank, rot_dim, q_weight, kv_weight, eps, positions, inv_freq,
+                               rotary_dim, q_latent, pool, slots, pool_rows, error_word, dtype, 0, 1.0f, stream);
 }
 
 // out[r, h, out_offset + i] = rotated(x[r, h, in_offset + i]) for i < width; entries from rotary_dim on are copied.
@@ -105,7 +119,7 @@ template <typename T>
 __global__ void rope_slice_kernel(const T* __restrict__ x, size_t x_row, size_t x_head, int in_offset,
                                   T* __restrict__ out, size_t out_row, size_t out_head, int out_offset, int heads,
                                   int width, int rotary_dim, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq) {
+                                  const float* __restrict__ inv_freq, int interleaved, float magnitude) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int row = blockIdx.x;
@@ -119,18 +133,21 @@ __global__ void rope_slice_kernel(const T* __restrict__ x, size_t x_row, size_t 
     if (i < half) {
       float sine, cosine;
       sincosf(position * inv_freq[i], &sine, &cosine);
-      const float u = srb_to_float(src[i]), v = srb_to_float(src[i + half]);
-      dst[i] = srb_from_float<T>(u * cosine - v * sine);
-      dst[i + half] = srb_from_float<T>(v * cosine + u * sine);
+      sine *= magnitude; cosine *= magnitude;
+      const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+      const float u = srb_to_float(src[ia]), v = srb_to_float(src[ib]);
+      dst[ia] = srb_from_float<T>(u * cosine - v * sine);
+      dst[ib] = srb_from_float<T>(v * cosine + u * sine);
     } else {
       dst[rotary_dim + i - half] = src[rotary_dim + i - half];
     }
   }
 }
 
-extern "C" int srb_rope_slice(const void* x, long long x_row, long long x_head, int in_offset, void* out,
-                              long long out_row, long long out_head, int out_offset, int rows, int heads, int width,
-                              int rotary_dim, const int* positions, const float* inv_freq, int dtype, void* stream) {
+extern "C" int srb_rope_slice_ex(const void* x, long long x_row, long long x_head, int in_offset, void* out,
+                                 long long out_row, long long out_head, int out_offset, int rows, int heads, int width,
+                                 int rotary_dim, const int* positions, const float* inv_freq, int dtype, int interleaved,
+                                 float magnitude, void* stream) {
   if (rows <= 0 || heads <= 0 || width <= 0) return SRB_OK;
   if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > width)
     SRB_FAIL("rope_slice: %d rotated entries must be even and at most the slice (%d)", rotary_dim, width);
@@ -139,15 +156,23 @@ extern "C" int srb_rope_slice(const void* x, long long x_row, long long x_head, 
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(rope_slice_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)x, (size_t)x_row,
                              (size_t)x_head, in_offset, (float*)out, (size_t)out_row, (size_t)out_head, out_offset, heads,
-                             width, rotary_dim, positions, inv_freq));
+                             width, rotary_dim, positions, inv_freq, interleaved, magnitude));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(rope_slice_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, s, (const __nv_bfloat16*)x,
                              (size_t)x_row, (size_t)x_head, in_offset, (__nv_bfloat16*)out, (size_t)out_row,
-                             (size_t)out_head, out_offset, heads, width, rotary_dim, positions, inv_freq));
+                             (size_t)out_head, out_offset, heads, width, rotary_dim, positions, inv_freq, interleaved,
+                             magnitude));
   else
     SRB_FAIL("rope_slice: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("rope_slice");
   return SRB_OK;
+}
+
+extern "C" int srb_rope_slice(const void* x, long long x_row, long long x_head, int in_offset, void* out,
+                              long long out_row, long long out_head, int out_offset, int rows, int heads, int width,
+                              int rotary_dim, const int* positions, const float* inv_freq, int dtype, void* stream) {
+  return srb_rope_slice_ex(x, x_row, x_head, in_offset, out, out_row, out_head, out_offset, rows, heads, width, rotary_dim,
+                           positions, inv_freq, dtype, 0, 1.0f, stream);
 }
 
 // ---- one matrix per head ------------------------------------------------------------------------------
@@ -160,7 +185,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const T* __restrict__ x, size_t x_row, size_t x_head, const T* __restrict__ w, T* __restrict__ out,
                    size_t out_row, size_t out_head, int rows, int n_in, int n_out, const T* __restrict__ gate,
-                   size_t gate_row) {
+                   size_t gate_row, int gate_head, int gate_col) {
   __shared__ float x_tile[HL_K][HL_TILE + 4];
   __shared__ float w_tile[HL_K][HL_TILE + 4];
   srb_launch_dependents();
@@ -197,12 +222,13 @@ head_linear_kernel(const T* __restrict__ x, size_t x_row, size_t x_head, const T
   for (int i = 0; i < 4; ++i) {
     const int r = row0 + ty * 4 + i;
     if (r >= rows) continue;
-    float g = 1.f;
-    if (gate) g = 1.0f / (1.0f + expf(-srb_to_float(gate[(size_t)r * gate_row + head])));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = col0 + tx * 4 + j;
-      if (c < n_out) out[(size_t)r * out_row + (size_t)head * out_head + c] = srb_from_float<T>(acc[i][j] * g);
+      if (c >= n_out) continue;
+      float g = 1.f;
+      if (gate) g = 1.0f / (1.0f + expf(-srb_to_float(gate[(size_t)r * gate_row + (size_t)head * gate_head + (size_t)c * gate_col])));
+      out[(size_t)r * out_row + (size_t)head * out_head + c] = srb_from_float<T>(acc[i][j] * g);
     }
   }
 }
@@ -211,7 +237,7 @@ head_linear_kernel(const T* __restrict__ x, size_t x_row, size_t x_head, const T
 __global__ void __launch_bounds__(128)
 head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t x_head, const __nv_bfloat16* __restrict__ w,
                        __nv_bfloat16* __restrict__ out, size_t out_row, size_t out_head, int rows, int n_in, int n_out,
-                       const __nv_bfloat16* __restrict__ gate, size_t gate_row) {
+                       const __nv_bfloat16* __restrict__ gate, size_t gate_row, int gate_head, int gate_col) {
   __shared__ __align__(16) TileMmaSmem s;
   srb_launch_dependents();
   srb_grid_dependency_wait();
@@ -229,13 +255,16 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t
       const int r = row0 + tile_mma_row(i, c2 * 2);
       if (r >= rows) continue;
       float g = 1.f;
-      if (gate) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + head])));
+      if (gate && !gate_col) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + (size_t)head * gate_head])));
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int c1 = 0; c1 < 2; ++c1) {
           const int col = col0 + tile_mma_col(j, c1);
-          if (col < n_out) out[(size_t)r * out_row + (size_t)head * out_head + col] = __float2bfloat16_rn(acc[0][i][j][c2 * 2 + c1] * g);
+          if (col >= n_out) continue;
+          if (gate && gate_col)
+            g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + (size_t)head * gate_head + (size_t)col * gate_col])));
+          out[(size_t)r * out_row + (size_t)head * out_head + col] = __float2bfloat16_rn(acc[0][i][j][c2 * 2 + c1] * g);
         }
     }
 }
@@ -244,7 +273,7 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t
 __global__ void __launch_bounds__(256)
 head_linear_async_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size_t x_head, const __nv_bfloat16* __restrict__ w,
                          __nv_bfloat16* __restrict__ out, size_t out_row, size_t out_head, int rows, int n_in, int n_out,
-                         const __nv_bfloat16* __restrict__ gate, size_t gate_row) {
+                         const __nv_bfloat16* __restrict__ gate, size_t gate_row, int gate_head, int gate_col) {
   extern __shared__ __align__(16) unsigned char hl_smem[];
   TileAsyncSmem<1>& s = *reinterpret_cast<TileAsyncSmem<1>*>(hl_smem);
   srb_launch_dependents();
@@ -263,22 +292,26 @@ head_linear_async_kernel(const __nv_bfloat16* __restrict__ x, size_t x_row, size
       const int r = row0 + tile_async_row(i, c2 * 2);
       if (r >= rows) continue;
       float g = 1.f;
-      if (gate) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + head])));
+      if (gate && !gate_col) g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + (size_t)head * gate_head])));
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int c1 = 0; c1 < 2; ++c1) {
           const int col = col0 + tile_async_col(j, c1);
-          if (col < n_out) out[(size_t)r * out_row + (size_t)head * out_head + col] = __float2bfloat16_rn(acc[0][i][j][c2 * 2 + c1] * g);
+          if (col >= n_out) continue;
+          if (gate && gate_col)
+            g = 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)r * gate_row + (size_t)head * gate_head + (size_t)col * gate_col])));
+          out[(size_t)r * out_row + (size_t)head * out_head + col] = __float2bfloat16_rn(acc[0][i][j][c2 * 2 + c1] * g);
         }
     }
 }
 
 // x: rows x_row elements apart, heads x_head apart; w: [heads, n_out, n_in]; out likewise by out_row / out_head.
-// gate (optional): gate[r * gate_row + h] is a logit; the head's result is multiplied by its sigmoid.
-extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head, const void* w, void* out,
-                               long long out_row, long long out_head, int rows, int heads, int n_in, int n_out,
-                               const void* gate, long long gate_row, int dtype, void* stream) {
+// gate (optional): gate[r * gate_row + h * gate_head + o * gate_col] is a logit; the result out[r, h, o] is multiplied by
+// its sigmoid (gate_head 1, gate_col 0: one gate per head; gate_head n_out, gate_col 1: one per entry).
+extern "C" int srb_head_linear_ex(const void* x, long long x_row, long long x_head, const void* w, void* out,
+                                  long long out_row, long long out_head, int rows, int heads, int n_in, int n_out,
+                                  const void* gate, long long gate_row, int gate_head, int gate_col, int dtype, void* stream) {
   if (rows <= 0 || heads <= 0 || n_out <= 0) return SRB_OK;
   if (n_in <= 0) SRB_FAIL("head_linear: inner size %d must be positive", n_in);
   dim3 grid((n_out + HL_TILE - 1) / HL_TILE, (rows + HL_TILE - 1) / HL_TILE, heads);
@@ -287,7 +320,7 @@ extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head,
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(head_linear_kernel<float>, grid, dim3(256), 0, s, (const float*)x, (size_t)x_row,
                              (size_t)x_head, (const float*)w, (float*)out, (size_t)out_row, (size_t)out_head, rows, n_in,
-                             n_out, (const float*)gate, (size_t)gate_row));
+                             n_out, (const float*)gate, (size_t)gate_row, gate_head, gate_col));
   else if (dtype == SRB_DTYPE_BF16 && n_in % 8 == 0 && x_row % 8 == 0 && x_head % 8 == 0 &&
            (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
     grid.y = (rows + TA_ROWS - 1) / TA_ROWS;
@@ -295,13 +328,20 @@ extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head,
                                        (int)sizeof(TileAsyncSmem<1>)));
     SRB_CUDA_CALL(srb_launch(head_linear_async_kernel, grid, dim3(256), sizeof(TileAsyncSmem<1>), s, (const __nv_bfloat16*)x,
                              (size_t)x_row, (size_t)x_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (size_t)out_row,
-                             (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row));
+                             (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row, gate_head, gate_col));
   } else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(head_linear_mma_kernel, grid, dim3(128), 0, s, (const __nv_bfloat16*)x,
                              (size_t)x_row, (size_t)x_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, (size_t)out_row,
-                             (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row));
+                             (size_t)out_head, rows, n_in, n_out, (const __nv_bfloat16*)gate, (size_t)gate_row, gate_head, gate_col));
   else
     SRB_FAIL("head_linear: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("head_linear");
   return SRB_OK;
+}
+
+extern "C" int srb_head_linear(const void* x, long long x_row, long long x_head, const void* w, void* out,
+                               long long out_row, long long out_head, int rows, int heads, int n_in, int n_out,
+                               const void* gate, long long gate_row, int dtype, void* stream) {
+  return srb_head_linear_ex(x, x_row, x_head, w, out, out_row, out_head, rows, heads, n_in, n_out, gate, gate_row, 1, 0, dtype,
+                            stream);
 }

@@ -602,10 +602,13 @@ extern "C" int srb_moe_down(const void* act, const void* w_down, const int* plan
 }
 
 // `base` (float [rows, width], or null): a term that every row gets beside its experts' (an expert that all rows share);
-// it is the first term of the sum.
+// it is the first term of the sum.  `chosen` and `input` (both or neither): a choice whose number is `experts` or more
+// names an expert that returns its input, so its term is weight * input[row] (such choices have no slot in the plan).
+template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ entry_slot,
                                    const float* __restrict__ weights, int top, int width, float* __restrict__ out,
-                                   const float* __restrict__ base) {
+                                   const float* __restrict__ base, const int* __restrict__ chosen, int experts,
+                                   const T* __restrict__ input) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int row = blockIdx.x;
@@ -614,18 +617,34 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (int k = 0; k < top; ++k) {
       const int slot = entry_slot[(size_t)row * top + k];
       if (slot >= 0) sum += weights[(size_t)row * top + k] * y[(size_t)slot * width + i];
+      else if (input && chosen[(size_t)row * top + k] >= experts)
+        sum += weights[(size_t)row * top + k] * srb_to_float(input[(size_t)row * width + i]);
     }
     out[(size_t)row * width + i] = sum;
   }
 }
 
-extern "C" int srb_moe_combine_onto(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
-                                    float* out, const float* base, void* stream) {
+extern "C" int srb_moe_combine_identity(const float* y, const int* entry_slot, const float* weights, int rows, int top,
+                                        int width, float* out, const float* base, const int* chosen, int experts,
+                                        const void* input, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
-  SRB_CUDA_CALL(srb_launch(moe_combine_kernel, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, y,
-                           entry_slot, weights, top, width, out, base));
+  if ((chosen == nullptr) != (input == nullptr)) SRB_FAIL("moe_combine: the choices and the experts' input come together");
+  const dim3 block(width >= 1024 ? 256 : 128);
+  if (dtype == SRB_DTYPE_F32)
+    SRB_CUDA_CALL(srb_launch(moe_combine_kernel<float>, dim3(rows), block, 0, (cudaStream_t)stream, y, entry_slot, weights, top,
+                             width, out, base, chosen, experts, (const float*)input));
+  else if (dtype == SRB_DTYPE_BF16)
+    SRB_CUDA_CALL(srb_launch(moe_combine_kernel<__nv_bfloat16>, dim3(rows), block, 0, (cudaStream_t)stream, y, entry_slot,
+                             weights, top, width, out, base, chosen, experts, (const __nv_bfloat16*)input));
+  else
+    SRB_FAIL("moe_combine: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("moe_combine");
   return SRB_OK;
+}
+
+extern "C" int srb_moe_combine_onto(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
+                                    float* out, const float* base, void* stream) {
+  return srb_moe_combine_identity(y, entry_slot, weights, rows, top, width, out, base, nullptr, 0, nullptr, SRB_DTYPE_F32, stream);
 }
 
 extern "C" int srb_moe_combine(const float* y, const int* entry_slot, const float* weights, int rows, int top, int width,
@@ -634,12 +653,15 @@ extern "C" int srb_moe_combine(const float* y, const int* entry_slot, const floa
 }
 
 // rows of h in slot order: out[slot, :] = h[slot_row[slot], :] (16 bytes a thread where the rows allow it), for
-// products that take their operands as whole tiles of consecutive rows
+// products that take their operands as whole tiles of consecutive rows.  `used` (or null) points at the number of slots
+// that the plan handed out (its last offset): choices without a slot leave the slots behind it without a row.
 template <typename T>
-__global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ slot_row, int width, T* __restrict__ out) {
+__global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict__ slot_row, int width, T* __restrict__ out,
+                                  const int* __restrict__ used) {
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int slot = blockIdx.x;
+  if (used && slot >= *used) return;
   const T* src = h + (size_t)slot_row[slot] * width;
   T* dst = out + (size_t)slot * width;
   if ((width * sizeof(T)) % 16 == 0 && (((uintptr_t)h | (uintptr_t)out) & 15) == 0) {
@@ -651,14 +673,21 @@ __global__ void moe_gather_kernel(const T* __restrict__ h, const int* __restrict
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
 }
 
+extern "C" int srb_moe_gather_used(const void* h, const int* slot_row, int slots, int width, void* out, const int* used,
+                                   int dtype, void* stream);
 extern "C" int srb_moe_gather(const void* h, const int* slot_row, int slots, int width, void* out, int dtype, void* stream) {
+  return srb_moe_gather_used(h, slot_row, slots, width, out, nullptr, dtype, stream);
+}
+
+extern "C" int srb_moe_gather_used(const void* h, const int* slot_row, int slots, int width, void* out, const int* used,
+                                   int dtype, void* stream) {
   if (slots <= 0 || width <= 0) return SRB_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    SRB_CUDA_CALL(srb_launch(moe_gather_kernel<float>, dim3(slots), dim3(128), 0, s, (const float*)h, slot_row, width, (float*)out));
+    SRB_CUDA_CALL(srb_launch(moe_gather_kernel<float>, dim3(slots), dim3(128), 0, s, (const float*)h, slot_row, width, (float*)out, used));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(moe_gather_kernel<__nv_bfloat16>, dim3(slots), dim3(128), 0, s, (const __nv_bfloat16*)h, slot_row,
-                             width, (__nv_bfloat16*)out));
+                             width, (__nv_bfloat16*)out, used));
   else
     SRB_FAIL("moe_gather: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("moe_gather");

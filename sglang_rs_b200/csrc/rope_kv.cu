@@ -639,3 +639,135 @@ extern "C" int srb_qk_norm_rope_kv_ex(const void* qkv, const float* qkv_parts, i
   SRB_LAUNCH_CHECK("qk_norm_rope_kv");
   return SRB_OK;
 }
+
+// ---- norms over whole projections ---------------------------------------------------------------------------------
+// Another arrangement of the same step: q and k are each divided by the root mean square of the WHOLE projection (all
+// heads of the row together, before they are split into heads) and multiplied by a weight per entry of the projection;
+// then each head's leading `rotary_dim` entries are rotated, q goes to `q_out`, k into the pages.  Values may have a
+// width of their own (`value_dim`; the value pool is [pages, n_kv, page_size, value_dim]) and are stored as projected.
+// Behind the values the projection may hold `gate_cols` logits of an output gate: their sigmoids are written, in
+// 32-bit, to `gate_out` [rows, gate_cols] for the attention kernel that multiplies its result by them.
+// Row of the projection: [n_q * head_dim | n_kv * head_dim | n_kv * value_dim | gate_cols].
+// One block per row; sums of squares, norms, angles and the rotation are 32-bit; a norm whose weight is null is left out.
+template <typename T>
+__global__ void __launch_bounds__(256)
+proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_parts, int num_parts, size_t part_stride,
+                         int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                         float* __restrict__ gate_out, const int* __restrict__ positions, const int* __restrict__ slots,
+                         const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps,
+                         const float* __restrict__ inv_freq, int rotary_dim, int interleaved, float magnitude, int n_q,
+                         int n_kv, int head_dim, int value_dim, int gate_cols, int page_size, int num_pages,
+                         int* error_word) {
+  extern __shared__ __align__(16) float staged[];       // (n_q + n_kv) * head_dim values, rotary_dim cosines and sines, 33 of scratch
+  const int q_width = n_q * head_dim, k_width = n_kv * head_dim;
+  float* cos_table = staged + q_width + k_width;
+  float* sin_table = cos_table + (rotary_dim >> 1);
+  float* scratch = sin_table + (rotary_dim >> 1);
+  srb_launch_dependents();
+  const int row = blockIdx.x;
+  const int half = rotary_dim >> 1;
+  if (inv_freq) {                                        // needs the step's index arrays only: ahead of the wait
+    const float pos = (float)positions[row];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      float sn, cs;
+      sincosf(pos * inv_freq[i], &sn, &cs);
+      sin_table[i] = __fmul_rn(sn, magnitude);
+      cos_table[i] = __fmul_rn(cs, magnitude);
+    }
+  }
+  srb_grid_dependency_wait();
+  const size_t src = (size_t)row * qkv_stride;
+  auto value_at = [&](int column) -> float {
+    if (num_parts == 0) return srb_to_float(qkv[src + column]);
+    float x = 0.f;
+    for (int part = 0; part < num_parts; ++part) x += qkv_parts[part * part_stride + src + column];
+    return x;
+  };
+  float sum_q = 0.f, sum_k = 0.f;
+  for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
+    const float x = value_at(i);
+    staged[i] = x;
+    if (i < q_width) sum_q = __fmaf_rn(x, x, sum_q); else sum_k = __fmaf_rn(x, x, sum_k);
+  }
+  const float inv_q = q_weight ? 1.0f / sqrtf(srb_block_sum(sum_q, scratch) / (float)q_width + eps) : 1.f;
+  const float inv_k = k_weight ? 1.0f / sqrtf(srb_block_sum(sum_k, scratch) / (float)k_width + eps) : 1.f;
+  for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
+    if (i < q_width) { if (q_weight) staged[i] = normed(staged[i], inv_q, q_weight[i]); }
+    else if (k_weight) staged[i] = normed(staged[i], inv_k, k_weight[i - q_width]);
+  }
+  __syncthreads();
+  if (inv_freq) {
+    for (int item = threadIdx.x; item < (n_q + n_kv) * half; item += blockDim.x) {
+      const int head = item / half, i = item - head * half;
+      float* v = staged + (size_t)head * head_dim;
+      const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+      const float a = v[ia], b = v[ib], cs = cos_table[i], sn = sin_table[i];
+      v[ia] = rotate_first(a, b, cs, sn);
+      v[ib] = rotate_second(a, b, cs, sn);
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < q_width; i += blockDim.x) q_out[(size_t)row * q_width + i] = srb_from_float<T>(staged[i]);
+  if (gate_out)
+    for (int i = threadIdx.x; i < gate_cols; i += blockDim.x)
+      gate_out[(size_t)row * gate_cols + i] = 1.0f / (1.0f + expf(-value_at(q_width + k_width + n_kv * value_dim + i)));
+  if (!slots) return;
+  const int slot = slots[row];
+  if (slot < 0 || slot >= num_pages * page_size) {
+    if (threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+    return;
+  }
+  const size_t page = slot / page_size, inside = slot % page_size;
+  for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
+    const int head = i / head_dim, e = i - head * head_dim;
+    k_pool[((page * n_kv + head) * page_size + inside) * head_dim + e] = srb_from_float<T>(staged[q_width + i]);
+  }
+  for (int i = threadIdx.x; i < n_kv * value_dim; i += blockDim.x) {
+    const int head = i / value_dim, e = i - head * value_dim;
+    v_pool[((page * n_kv + head) * page_size + inside) * value_dim + e] = srb_from_float<T>(value_at(q_width + k_width + i));
+  }
+}
+
+extern "C" int srb_proj_norm_rope_kv(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
+                                     int qkv_stride, void* q_out, void* k_pool, void* v_pool, float* gate_out,
+                                     const int* positions, const int* slots, const float* q_weight, const float* k_weight,
+                                     float eps, const float* inv_freq, int rotary_dim, int interleaved, float magnitude,
+                                     int rows, int n_q, int n_kv, int head_dim, int value_dim, int gate_cols, int page_size,
+                                     int num_pages, int* error_word, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (n_q <= 0 || n_kv <= 0 || head_dim <= 0 || value_dim <= 0 || page_size <= 0 || gate_cols < 0)
+    SRB_FAIL("proj_norm_rope_kv: head counts, widths and page size must be positive");
+  if (inv_freq && (rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1)))
+    SRB_FAIL("proj_norm_rope_kv: rotary width %d must be even, positive and at most head_dim %d", rotary_dim, head_dim);
+  if (!inv_freq) rotary_dim = 0;
+  if (num_parts < 0 || (num_parts > 0 && !qkv_parts) || (num_parts == 0 && !qkv))
+    SRB_FAIL("proj_norm_rope_kv: the projection is missing");
+  if ((long long)qkv_stride < (long long)(n_q + n_kv) * head_dim + (long long)n_kv * value_dim + gate_cols)
+    SRB_FAIL("proj_norm_rope_kv: rows of the projection are narrower than their parts together");
+  if (gate_cols > 0 && !gate_out) SRB_FAIL("proj_norm_rope_kv: gate logits without a place for the gates");
+  if (!(eps >= 0.f)) SRB_FAIL("proj_norm_rope_kv: eps must be finite and non-negative");
+  const size_t smem = ((size_t)(n_q + n_kv) * head_dim + rotary_dim + 33) * sizeof(float);
+  if (smem > 227 * 1024) SRB_FAIL("proj_norm_rope_kv: %zu bytes of shared memory exceed 232448", smem);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32) {
+    if (smem > 48 * 1024)
+      SRB_CUDA_CALL(cudaFuncSetAttribute(proj_norm_rope_kv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SRB_CUDA_CALL(srb_launch(proj_norm_rope_kv_kernel<float>, dim3(rows), dim3(256), smem, s, (const float*)qkv, qkv_parts,
+                             num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool,
+                             gate_out, positions, slots, q_weight, k_weight, eps, inv_freq, rotary_dim, interleaved,
+                             magnitude, n_q, n_kv, head_dim, value_dim, gate_cols, page_size, num_pages, error_word));
+  } else if (dtype == SRB_DTYPE_BF16) {
+    if (smem > 48 * 1024)
+      SRB_CUDA_CALL(cudaFuncSetAttribute(proj_norm_rope_kv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    SRB_CUDA_CALL(srb_launch(proj_norm_rope_kv_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, s,
+                             (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
+                             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, gate_out, positions, slots,
+                             q_weight, k_weight, eps, inv_freq, rotary_dim, interleaved, magnitude, n_q, n_kv, head_dim,
+                             value_dim, gate_cols, page_size, num_pages, error_word));
+  } else {
+    SRB_FAIL("proj_norm_rope_kv: unknown dtype %d", dtype);
+  }
+  SRB_LAUNCH_CHECK("proj_norm_rope_kv");
+  return SRB_OK;
+}

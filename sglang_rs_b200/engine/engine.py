@@ -25,7 +25,7 @@ from .scheduler import Request, Scheduler, SchedulerConfig, StepOutput
 
 def kv_bytes_per_token(model, dtype: torch.dtype) -> int:
     from ..parts.base import PagedKV
-    width = sum((2 if need.values else 1) * need.num_kv_heads * need.head_dim for need in model.cache_needs()
+    width = sum(need.num_kv_heads * (need.head_dim + need.value_width) for need in model.cache_needs()
                 if isinstance(need, PagedKV))
     return width * (4 if dtype == torch.float32 else 2)
 

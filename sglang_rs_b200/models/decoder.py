@@ -97,8 +97,11 @@ class DecoderModel(Part):
         delta = None
         origin = None
         if any(call.entry is not None for call in self.program):
-            # the embedding output as the pass entries read it; layers ahead of the first pass change the stream in place
-            origin = residual if self.program[0].entry is not None else residual.clone()
+            # the embedding output as the pass entries read it; layers ahead of the first pass change the stream in
+            # place, and so does an entry that adds onto the stream it is given
+            first_makes_new = self.program[0].entry is not None and not getattr(
+                self.pass_entries[self.program[0].entry], "in_place", False)
+            origin = residual if first_makes_new else residual.clone()
         for index, call in enumerate(self.program):
             cache = caches[index if call.cache_from is None else call.cache_from]
             if call.cache_from is not None and cache is not None:

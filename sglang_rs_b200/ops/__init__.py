@@ -210,8 +210,9 @@ NORM_KINDS = {"none": 0, "rms": 1, "layer": 2}
 @traced("norm")
 def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, outer, out: Optional[torch.Tensor],
                   row_index: Optional[torch.Tensor] = None, write_residual: bool = True,
-                  extra: Optional[torch.Tensor] = None) -> None:
-    """x = residual + inner(delta); residual = x if asked; out = outer(x), all sums and means in 32-bit.
+                  extra: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None) -> None:
+    """x = residual + inner(delta) (+ addend); residual = x if asked; out = outer(x), all sums and means in 32-bit.
+    ``addend`` (float32, shaped like the residual) is a second term of the sum, added after the pending one.
 
     ``inner`` and ``outer`` are ``(kind, weight, bias, eps)`` with kind one of ``NORM_KINDS`` (``none``: the
     identity; ``rms``: v / sqrt(mean(v^2) + eps) * w; ``layer``: (v - mean) / sqrt(var + eps) * w + b) or None
@@ -262,14 +263,18 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
         _need(extra, "extra", torch.float32)
         if extra.shape != residual.shape:
             raise KernelError("norm_add_norm: extra and residual differ in shape")
+    if addend is not None:
+        _need(addend, "addend", torch.float32)
+        if addend.shape != residual.shape:
+            raise KernelError("norm_add_norm: addend and residual differ in shape")
     if row_index is not None:
         _need(row_index, "row_index", torch.int32)
     lib = load_library("elementwise")
-    _check(lib, lib.srb_norm_add_norm_ex(
+    _check(lib, lib.srb_norm_add_norm_plus(
         _ptr(residual), _ptr(whole), _ptr(as_float), inner_kind, _ptr(inner_w), _ptr(inner_b), ctypes.c_float(inner_eps),
         inner_groups, ctypes.c_float(inner_scale), outer_kind, _ptr(outer_w), _ptr(outer_b), ctypes.c_float(outer_eps),
         outer_groups, ctypes.c_float(outer_scale), _ptr(out), ctypes.c_longlong(pitch),
-        _ptr(extra), _ptr(row_index), rows, width, int(write_residual), dtype_code(dtype), _stream()))
+        _ptr(extra), _ptr(row_index), rows, width, int(write_residual), dtype_code(dtype), _ptr(addend), _stream()))
 
 
 #: activations of a gated feed-forward, act(gate) * up, by the numbers of csrc/activations.cuh
@@ -376,6 +381,63 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
 
 
 @traced("rope_kv")
+def proj_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                      positions: torch.Tensor, slots: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
+                      k_weight: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                      interleaved: bool, n_q: int, n_kv: int, head_dim: int, value_dim: int, error_word: torch.Tensor, *,
+                      magnitude: float = 1.0, gate_out: Optional[torch.Tensor] = None) -> None:
+    """The step between the q/k/v product and attention for a mixer that norms q and k over the WHOLE projection (all
+    heads of a row together, a weight per entry: ``q_weight`` [n_q * head_dim], ``k_weight`` [n_kv * head_dim]; None: no
+    norm), then rotates the leading ``rotary_dim`` entries of every head, writes q to ``q_out`` [rows, n_q, head_dim], k
+    into ``k_pool`` [pages, n_kv, page_size, head_dim] and the values, as projected, into ``v_pool`` [pages, n_kv,
+    page_size, value_dim].  Rows of ``qkv`` are [q | k | v | gate logits]; ``gate_out`` (float32 [rows, gates]) receives
+    the sigmoids of the logits behind the values.  ``qkv`` is of ``q_out``'s dtype or float32 [parts, rows, width]
+    partial sums.  ``slots`` None: nothing is stored."""
+    _need(qkv, "qkv"); _need(q_out, "q_out"); _need(positions, "positions", torch.int32)
+    whole = parts = None
+    num_parts = part_stride = 0
+    if qkv.dim() == 3:
+        _need(qkv, "qkv", torch.float32)
+        parts, num_parts, part_stride = qkv, qkv.shape[0], qkv.stride(0)
+    else:
+        _need(qkv, "qkv", q_out.dtype)
+        whole = qkv
+    rows = qkv.shape[-2]
+    gate_cols = 0
+    if gate_out is not None:
+        _need(gate_out, "gate_out", torch.float32)
+        if gate_out.dim() != 2 or gate_out.shape[0] != rows:
+            raise KernelError("proj_norm_rope_kv: gate_out must be [rows, gates]")
+        gate_cols = gate_out.shape[1]
+    if qkv.shape[-1] < (n_q + n_kv) * head_dim + n_kv * value_dim + gate_cols:
+        raise KernelError("proj_norm_rope_kv: qkv is narrower than its parts together")
+    if q_out.shape != (rows, n_q, head_dim):
+        raise KernelError("proj_norm_rope_kv: q_out must be [rows, n_q, head_dim]")
+    page_size = num_pages = 1
+    if slots is not None:
+        _need(slots, "slots", torch.int32); _need(k_pool, "k_pool", q_out.dtype); _need(v_pool, "v_pool", q_out.dtype)
+        num_pages, pool_heads, page_size, pool_dim = k_pool.shape
+        if (pool_heads, pool_dim) != (n_kv, head_dim) or v_pool.shape != (num_pages, n_kv, page_size, value_dim):
+            raise KernelError("proj_norm_rope_kv: pools must be [pages, n_kv, page_size, head_dim] and [..., value_dim]")
+    for name, w, count in (("q_weight", q_weight, n_q * head_dim), ("k_weight", k_weight, n_kv * head_dim)):
+        if w is not None:
+            _need(w, name, torch.float32)
+            if w.numel() != count:
+                raise KernelError(f"proj_norm_rope_kv: {name} must have {count} entries")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("proj_norm_rope_kv: inv_freq must have rotary_dim / 2 entries")
+    lib = load_library("rope_kv")
+    _check(lib, lib.srb_proj_norm_rope_kv(
+        _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride), qkv.stride(-2), _ptr(q_out),
+        _ptr(k_pool) if slots is not None else None, _ptr(v_pool) if slots is not None else None, _ptr(gate_out),
+        _ptr(positions), _ptr(slots), _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(inv_freq), rotary_dim,
+        int(interleaved), ctypes.c_float(magnitude), rows, n_q, n_kv, head_dim, value_dim, gate_cols, page_size, num_pages,
+        _ptr(error_word), dtype_code(q_out.dtype), _stream()))
+
+
+@traced("rope_kv")
 def rope_table(positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
                angles: Optional[torch.Tensor] = None, magnitude: float = 1.0) -> torch.Tensor:
     """float32 [rows, rotary_dim]: per row the cosines, then the sines, of ``positions[r] * inv_freq[i]`` (or of
@@ -399,15 +461,17 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                     scale: float, window: int, split_size: int, max_splits: int,
                     scratch_acc: Optional[torch.Tensor], scratch_ml: Optional[torch.Tensor],
-                    error_word: torch.Tensor, sinks: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+                    error_word: torch.Tensor, sinks: Optional[torch.Tensor] = None, chunk: int = 0,
+                    gates: Optional[torch.Tensor] = None) -> None:
     """out[r, h, :] = softmax over the keys row r may see of (q . k) * scale, times v.
 
     A row at position p sees the keys max(0, p - window + 1) .. p (``window`` 0: from 0) and, with ``chunk`` > 0,
     of those only the keys of its own chunk of positions, floor(p / chunk) * chunk .. p.
 
     ``sinks`` (float32, one per query head): the softmax's denominator also holds exp(sink_h), a term without
-    key or value.  ``v_pool`` may hold rows narrower than the keys (``out`` is as wide as they are), and may be
-    None: the value of a key is then the first ``out.shape[2]`` entries of its key row.
+    key or value.  ``v_pool`` may hold rows of another width than the keys (``out`` is as wide as they are), and may be
+    None: the value of a key is then the first ``out.shape[2]`` entries of its key row.  ``gates`` (float32
+    [rows, n_q]): a factor on the result of every (row, query head).
 
     q, out: [rows, n_q, head_dim]; pools [pages, n_kv, page_size, head_dim]; block_table
     [requests, stride].  ``split_size`` 0 walks all keys in one block per (row, kv head);
@@ -419,8 +483,12 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     rows, n_q, head_dim = q.shape
     num_pages, n_kv, page_size, pool_dim = k_pool.shape
     value_dim = out.shape[2]
-    if pool_dim != head_dim or out.shape[:2] != q.shape[:2] or value_dim > head_dim:
+    if pool_dim != head_dim or out.shape[:2] != q.shape[:2] or (v_pool is None and value_dim > head_dim):
         raise KernelError("paged_attention: shapes of q, out and the pools do not agree")
+    if gates is not None:
+        _need(gates, "gates", torch.float32)
+        if gates.shape != (rows, n_q):
+            raise KernelError("paged_attention: one gate per row and query head is needed")
     if v_pool is not None:
         _need(v_pool, "v_pool", q.dtype)
         if v_pool.shape != (*k_pool.shape[:3], value_dim):
@@ -435,11 +503,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             raise KernelError("paged_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
     lib = load_library("attention")
-    _check(lib, lib.srb_paged_attention_masked(
+    _check(lib, lib.srb_paged_attention_gated(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
         _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
         num_pages, int(window), int(chunk), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
-        dtype_code(q.dtype), _ptr(sinks), value_dim, _stream()), launches=2 if split_size else 1)
+        dtype_code(q.dtype), _ptr(sinks), value_dim, _ptr(gates), _stream()), launches=2 if split_size else 1)
 
 
 
@@ -627,10 +695,13 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
 def latent_prepare(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: Optional[torch.Tensor],
                    kv_weight: torch.Tensor, eps: float, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
                    rotary_dim: int, q_latent: Optional[torch.Tensor], pool: Optional[torch.Tensor],
-                   slots: Optional[torch.Tensor], error_word: torch.Tensor) -> None:
+                   slots: Optional[torch.Tensor], error_word: torch.Tensor, interleaved: bool = False,
+                   magnitude: float = 1.0) -> None:
     """Rows of ``proj`` hold [query latent (q_rank) | key/value latent (kv_rank) | shared key part (rot_dim) | ...].
     ``q_latent[r]`` = RMS norm of the first; the row's slot of ``pool`` ([pages, 1, page_size, kv_rank + rot_dim])
-    receives the RMS norm of the second and the rotated third.  ``slots`` None: nothing is stored."""
+    receives the RMS norm of the second and the rotated third.  ``slots`` None: nothing is stored.  The rotation pairs
+    entry i with entry i + rotary_dim / 2, or, with ``interleaved``, entry 2i with 2i + 1; ``magnitude`` multiplies the
+    cosines and sines."""
     _need(positions, "positions", torch.int32); _need(kv_weight, "kv_weight", torch.float32)
     if proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
         raise KernelError("latent_prepare: proj must be a CUDA matrix with dense rows")
@@ -652,17 +723,20 @@ def latent_prepare(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, 
         if inv_freq.numel() != rotary_dim // 2:
             raise KernelError("latent_prepare: inv_freq must have rotary_dim / 2 entries")
     lib = load_library("latent")
-    _check(lib, lib.srb_latent_prepare(
+    _check(lib, lib.srb_latent_prepare_ex(
         _ptr(proj), ctypes.c_longlong(proj.stride(0)), rows, q_rank, kv_rank, rot_dim, _ptr(q_weight), _ptr(kv_weight),
         ctypes.c_float(eps), _ptr(positions), _ptr(inv_freq), rotary_dim, _ptr(q_latent), _ptr(pool), _ptr(slots),
-        ctypes.c_longlong(pool_rows), _ptr(error_word), dtype_code(proj.dtype), _stream()))
+        ctypes.c_longlong(pool_rows), _ptr(error_word), dtype_code(proj.dtype), int(interleaved), ctypes.c_float(magnitude),
+        _stream()))
 
 
 @traced("rope_slice")
 def rope_slice(x: torch.Tensor, in_offset: int, out: torch.Tensor, out_offset: int, width: int, rotary_dim: int,
-               positions: torch.Tensor, inv_freq: Optional[torch.Tensor]) -> None:
-    """out[r, h, out_offset + i] = rotated(x[r, h, in_offset + i]), i < width, pairs (i, i + rotary_dim / 2);
-    entries from ``rotary_dim`` on are copied.  x, out: [rows, heads, *] with dense last axis."""
+               positions: torch.Tensor, inv_freq: Optional[torch.Tensor], interleaved: bool = False,
+               magnitude: float = 1.0) -> None:
+    """out[r, h, out_offset + i] = rotated(x[r, h, in_offset + i]), i < width, pairs (i, i + rotary_dim / 2) or, with
+    ``interleaved``, (2i, 2i + 1); ``magnitude`` multiplies the cosines and sines; entries from ``rotary_dim`` on are
+    copied.  x, out: [rows, heads, *] with dense last axis."""
     _need(x, "x"); _need(out, "out", x.dtype); _need(positions, "positions", torch.int32)
     if x.dim() != 3 or out.dim() != 3 or x.shape[:2] != out.shape[:2]:
         raise KernelError("rope_slice: x and out must be [rows, heads, *]")
@@ -673,17 +747,20 @@ def rope_slice(x: torch.Tensor, in_offset: int, out: torch.Tensor, out_offset: i
         if inv_freq.numel() != rotary_dim // 2:
             raise KernelError("rope_slice: inv_freq must have rotary_dim / 2 entries")
     lib = load_library("latent")
-    _check(lib, lib.srb_rope_slice(
+    _check(lib, lib.srb_rope_slice_ex(
         _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), in_offset, _ptr(out),
         ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)), out_offset, x.shape[0], x.shape[1], width,
-        rotary_dim, _ptr(positions), _ptr(inv_freq), dtype_code(x.dtype), _stream()))
+        rotary_dim, _ptr(positions), _ptr(inv_freq), dtype_code(x.dtype), int(interleaved), ctypes.c_float(magnitude),
+        _stream()))
 
 
 @traced("head_linear")
-def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
+def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                gate_per_entry: bool = False) -> None:
     """out[r, h, :n_out] = weight[h] @ x[r, h, :n_in] with ``weight`` [heads, n_out, n_in]; x and out are views
     [rows, heads, >= n] with a dense last axis.  ``gate`` ([rows, >= heads] view of logits): head h's result is
-    multiplied by sigmoid(gate[r, h])."""
+    multiplied by sigmoid(gate[r, h]); with ``gate_per_entry`` the gate is [rows, >= heads * n_out] and entry o of head
+    h is multiplied by sigmoid(gate[r, h * n_out + o])."""
     heads, n_out, n_in = weight.shape
     _need(weight, "weight", x.dtype)
     if (x.dim() != 3 or out.dim() != 3 or x.shape[1] != heads or out.shape[1] != heads or x.shape[0] != out.shape[0]
@@ -691,14 +768,16 @@ def head_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: 
         raise KernelError("head_linear: x, weight and out do not fit")
     gate_row = 0
     if gate is not None:
-        if gate.dim() != 2 or gate.shape[0] != x.shape[0] or gate.shape[1] < heads or gate.stride(1) != 1 or gate.dtype != x.dtype:
-            raise KernelError("head_linear: gate must be [rows, heads] of x's dtype with a dense last axis")
+        gates = heads * (n_out if gate_per_entry else 1)
+        if gate.dim() != 2 or gate.shape[0] != x.shape[0] or gate.shape[1] < gates or gate.stride(1) != 1 or gate.dtype != x.dtype:
+            raise KernelError("head_linear: gate must be [rows, heads (times entries)] of x's dtype with a dense last axis")
         gate_row = gate.stride(0)
     lib = load_library("latent")
-    _check(lib, lib.srb_head_linear(
+    _check(lib, lib.srb_head_linear_ex(
         _ptr(x), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(x.stride(1)), _ptr(weight), _ptr(out),
         ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)), x.shape[0], heads, n_in, n_out, _ptr(gate),
-        ctypes.c_longlong(gate_row), dtype_code(x.dtype), _stream()))
+        ctypes.c_longlong(gate_row), n_out if gate_per_entry else 1, 1 if gate_per_entry else 0, dtype_code(x.dtype),
+        _stream()))
 
 
 # --------------------------------------------------------------------------- routed experts
@@ -720,8 +799,12 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
                    activation: str, renormalize: bool, error_word: torch.Tensor, *, gated: bool = True,
                    router_bias: Optional[torch.Tensor] = None, base: Optional[torch.Tensor] = None,
                    scoring: str = "softmax", choice_bias: Optional[torch.Tensor] = None, weight_scale: float = 1.0,
-                   norm_eps: float = 0.0, activation_param: float = 0.0) -> torch.Tensor:
+                   norm_eps: float = 0.0, activation_param: float = 0.0, identity: int = 0) -> torch.Tensor:
     """sum over the ``top`` experts with the largest router scores of score * expert(h), float32 [rows, width].
+
+    ``identity``: the router has this many outputs more than there are expert matrices; they stand for experts that return
+    their input, so a row that chooses one gets weight * h[row] as that expert's term (the scores and the choice run over
+    all outputs alike; ``router``, ``router_bias`` and ``choice_bias`` have experts + identity rows).
 
     ``gated`` False: an expert is W_down act(W_up h) and ``w_gate_up`` holds the up matrices alone
     [experts, inner, width].  ``router_bias`` (float32 [experts]) is added to the router's logits before the choice.
@@ -743,21 +826,24 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     _need(h, "h"); _need(router, "router", h.dtype); _need(w_gate_up, "w_gate_up", h.dtype); _need(w_down, "w_down", h.dtype)
     rows, width = h.shape
     experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // (2 if gated else 1)
-    if (router.shape != (experts, width) or w_gate_up.shape != (experts, (2 if gated else 1) * inner, width)
+    routes = experts + int(identity)
+    if identity < 0 or routes > 1024:
+        raise KernelError(f"routed_experts: {routes} router outputs are outside what the router kernels take (1024)")
+    if (router.shape != (routes, width) or w_gate_up.shape != (experts, (2 if gated else 1) * inner, width)
             or w_down.shape != (experts, width, inner)):
         raise KernelError("routed_experts: shapes of the router and the experts do not agree")
     if router_bias is not None:
         _need(router_bias, "router_bias", torch.float32)
-        if router_bias.numel() != experts:
-            raise KernelError("routed_experts: one router bias per expert is needed")
+        if router_bias.numel() != routes:
+            raise KernelError("routed_experts: one router bias per router output is needed")
     if base is not None:
         _need(base, "base", torch.float32)
         if base.shape != (rows, width):
             raise KernelError("routed_experts: the shared term must be float32 [rows, width]")
     if choice_bias is not None:
         _need(choice_bias, "choice_bias", torch.float32)
-        if choice_bias.numel() != experts:
-            raise KernelError("routed_experts: one choice bias per expert is needed")
+        if choice_bias.numel() != routes:
+            raise KernelError("routed_experts: one choice bias per router output is needed")
     rule = (int(renormalize), ROUTER_SCORING[scoring], _ptr(choice_bias), ctypes.c_float(weight_scale), ctypes.c_float(norm_eps))
     act_code, act_param = activation_code(activation, parametric=True), ctypes.c_float(activation_param)
     lib = load_library("moe")
@@ -778,10 +864,10 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
     if rows >= ROUTER_PRODUCT_MIN_ROWS or router_bias is not None:
         # many rows: the logits are a product like any other (32-bit accumulation, 32-bit result), the choice a kernel of its own
         logits = linear(h, router, router_bias, out_dtype=torch.float32, error_word=error_word)
-        _check(lib, lib.srb_moe_select_ex(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, experts, top, *rule,
+        _check(lib, lib.srb_moe_select_ex(_ptr(logits), ctypes.c_longlong(logits.stride(0)), rows, routes, top, *rule,
                                           _ptr(chosen), _ptr(weights), stream))
     else:
-        _check(lib, lib.srb_moe_route_ex(_ptr(h), _ptr(router), rows, width, experts, top, *rule, _ptr(chosen),
+        _check(lib, lib.srb_moe_route_ex(_ptr(h), _ptr(router), rows, width, routes, top, *rule, _ptr(chosen),
                                          _ptr(weights), code, stream))
     _check(lib, lib.srb_moe_plan_of(_ptr(chosen), rows, top, experts, tile_slots, _ptr(plan), _ptr(slot_row),
                                     _ptr(entry_slot), _ptr(error_word), stream))
@@ -789,7 +875,9 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
         product = load_library("gemm_bf16")
         max_tiles = lib.srb_moe_max_tiles_of(rows, top, experts, tile_slots)
         gathered = torch.empty((entries, width), dtype=h.dtype, device=device)
-        _check(lib, lib.srb_moe_gather(_ptr(h), _ptr(slot_row), entries, width, _ptr(gathered), code, stream))
+        # the plan's last offset is the number of slots handed out (choices of experts without tensors get none)
+        used = ctypes.c_void_p(plan.data_ptr() + 4 * (1 + experts))
+        _check(lib, lib.srb_moe_gather_used(_ptr(h), _ptr(slot_row), entries, width, _ptr(gathered), used, code, stream))
         _check(product, product.srb_gemm_bf16_grouped(
             _ptr(gathered), _ptr(w_gate_up), _ptr(act), _ptr(plan), max_tiles, tile_slots, entries, experts,
             (2 if gated else 1) * inner, inner, width, inner, inner if gated else 0, GEMM_MODES["gated" if gated else "act"],
@@ -809,8 +897,10 @@ def routed_experts(h: torch.Tensor, router: torch.Tensor, w_gate_up: torch.Tenso
                                            inner, act_code, act_param, _ptr(act), code, stream))
         _check(lib, lib.srb_moe_down(_ptr(act), _ptr(w_down), _ptr(plan), rows, top, experts, width, inner, _ptr(y), code,
                                      stream))
-    _check(lib, lib.srb_moe_combine_onto(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), _ptr(base),
-                                         stream))
+    # choices of `experts` and above have no slot in the plan: they are the experts that return their input
+    _check(lib, lib.srb_moe_combine_identity(_ptr(y), _ptr(entry_slot), _ptr(weights), rows, top, width, _ptr(out), _ptr(base),
+                                             _ptr(chosen) if identity else None, experts, _ptr(h) if identity else None, code,
+                                             stream))
     return out
 
 

@@ -13,6 +13,16 @@ projection and the value of a key is the key itself as projected, before the rot
 holds q and k only, and the fused kernel stores the unrotated key in the value pool); ``chunk`` makes a row
 see, of the keys up to its own, only those of its own chunk of ``chunk`` positions (chunks counted from
 position 0 of the sequence, whatever portion of a prompt brought the row).
+
+Four more, also off by default.  ``whole_norm``: q and k are each normed over the WHOLE projection (all heads of the row
+together, before they are split into heads) with a weight per entry of the projection, ``names.q_norm`` [n_q * head_dim]
+and ``names.k_norm`` [n_kv * head_dim], instead of head by head with a shared weight.  ``value_dim``: values of another
+width than queries and keys (W_v is [n_kv * value_dim, hidden], W_o [hidden, n_q * value_dim], the value pool has rows of
+that width).  ``sink``: a number that joins the softmax's denominator as exp(sink) beside the keys' terms, the same for
+every head (0 adds one to the denominator); it has no key and no value.  ``names.gate``: a matrix [n_q, hidden] whose
+product with the mixer's input gives a logit per head; head h's result is multiplied by its sigmoid before the output
+projection (the matrix rides in the q/k/v product, the factor in the attention kernel's last step).  A mixer with any of
+these runs ``ops.proj_norm_rope_kv`` and the generic attention kernel, which carry them.
 """
 from __future__ import annotations
 
@@ -37,6 +47,7 @@ class AttentionNames:
     k_bias: Optional[str] = None
     v_bias: Optional[str] = None
     o_bias: Optional[str] = None
+    gate: Optional[str] = None
 
 
 class GroupedQueryAttention(Mixer):
@@ -48,7 +59,8 @@ class GroupedQueryAttention(Mixer):
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  position: PositionEncoding, names: AttentionNames, *, qk_norm_eps: Optional[float] = None,
-                 window: Optional[int] = None, chunk: Optional[int] = None):
+                 window: Optional[int] = None, chunk: Optional[int] = None, whole_norm: bool = False,
+                 value_dim: Optional[int] = None, sink: Optional[float] = None, partial_sums: bool = True):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         if not 0 < head_dim <= self.MAX_HEAD_DIM:
@@ -65,27 +77,42 @@ class GroupedQueryAttention(Mixer):
         self.values_from_keys = names.v is None
         if self.values_from_keys and names.v_bias:
             raise ValueError("values that are the keys have no bias of their own")
-        self.w_qkv = self.w_o = self.b_qkv = self.b_o = self.q_norm = self.k_norm = None
+        self.whole_norm, self.sink = bool(whole_norm), None if sink is None else float(sink)
+        self.vd = int(value_dim) if value_dim is not None else self.d
+        if not 0 < self.vd <= 1024:
+            raise ValueError(f"values of {self.vd} entries are outside what the attention kernels take (1 to 1024)")
+        #: whether the output product may hand on partial sums along K (a consumer that cannot add them says no)
+        self.partial_sums = bool(partial_sums)
+        #: the arrangement that only ``ops.proj_norm_rope_kv`` and the generic attention kernel carry
+        self.wide = self.whole_norm or self.vd != self.d or self.sink is not None or names.gate is not None
+        if self.wide and (self.values_from_keys or names.q_bias or names.k_bias or names.v_bias):
+            raise ValueError("norms over whole projections, values of their own width, a sink and a gate are not built "
+                             "together with biases or with values that are the keys")
+        if self.whole_norm and (names.q_norm is None or names.k_norm is None):
+            raise ValueError("norms over whole projections need both weights")
+        self.w_qkv = self.w_o = self.b_qkv = self.b_o = self.q_norm = self.k_norm = self.sinks = None
 
     def cache_need(self) -> PagedKV:
-        return PagedKV(self.n_kv, self.d, self.window)
+        return PagedKV(self.n_kv, self.d, self.window, value_dim=None if self.vd == self.d else self.vd)
 
     def split_scratch(self):
-        return (self.n_q * self.d, self.n_q * 2)
+        return (self.n_q * self.vd, self.n_q * 2)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         n = self.names
         specs = {
             n.q: TensorSpec((self.n_q * self.d, self.hidden)),
             n.k: TensorSpec((self.n_kv * self.d, self.hidden)),
-            n.o: TensorSpec((self.hidden, self.n_q * self.d)),
+            n.o: TensorSpec((self.hidden, self.n_q * self.vd)),
         }
         if n.v:
-            specs[n.v] = TensorSpec((self.n_kv * self.d, self.hidden))
+            specs[n.v] = TensorSpec((self.n_kv * self.vd, self.hidden))
         if n.q_norm:
-            specs[n.q_norm] = TensorSpec((self.d,), "scale")
+            specs[n.q_norm] = TensorSpec((self.n_q * self.d if self.whole_norm else self.d,), "scale")
         if n.k_norm:
-            specs[n.k_norm] = TensorSpec((self.d,), "scale")
+            specs[n.k_norm] = TensorSpec((self.n_kv * self.d if self.whole_norm else self.d,), "scale")
+        if n.gate:
+            specs[n.gate] = TensorSpec((self.n_q, self.hidden))
         for name, width in ((n.q_bias, self.n_q * self.d), (n.k_bias, self.n_kv * self.d),
                             (n.v_bias, self.n_kv * self.d), (n.o_bias, self.hidden)):
             if name:
@@ -95,7 +122,8 @@ class GroupedQueryAttention(Mixer):
 
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         n = self.names
-        stacked = [tensors[n.q], tensors[n.k]] + ([tensors[n.v]] if n.v else [])
+        stacked = [tensors[n.q], tensors[n.k]] + ([tensors[n.v]] if n.v else []) + ([tensors[n.gate]] if n.gate else [])
+        self.sinks = torch.full((self.n_q,), self.sink, dtype=torch.float32, device=device) if self.sink is not None else None
         self.w_qkv = matrix_to(torch.cat(stacked, dim=0), device, dtype)
         self.w_o = matrix_to(tensors[n.o], device, dtype)
         self.q_norm = scale_to(tensors[n.q_norm], device) if n.q_norm else None
@@ -114,7 +142,7 @@ class GroupedQueryAttention(Mixer):
         kernel applies from a frequency table (an encoding that computes its angles in Python keeps the
         part-by-part path)."""
         from ..ops.records import SxAttention, linear_record
-        if self.w_qkv is None or not self.position.fused or self.values_from_keys or self.chunk:
+        if self.w_qkv is None or not self.position.fused or self.values_from_keys or self.chunk or self.wide:
             return None
         rotary = self.position.fused_rotary()
         if rotary is not None and (rotary.angles is not None or rotary.inv_freq is None or rotary.magnitude != 1.0):
@@ -135,6 +163,8 @@ class GroupedQueryAttention(Mixer):
         rotary = self.position.fused_rotary() if self.position.fused else None
         if not self.position.fused:
             raise NotImplementedError("a position encoding with kernels of its own is applied by its mixer")
+        if self.wide:
+            return self._forward_wide(ctx, cache, batch, qkv, q, rotary)
         ops.qk_norm_rope_kv(
             qkv, q, cache.k_pool if cache.writable else None, cache.v_pool if cache.writable else None,
             ctx.positions, batch.slots if cache.writable else None, self.q_norm, self.k_norm,
@@ -171,4 +201,29 @@ class GroupedQueryAttention(Mixer):
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
                                 scratch_ml=batch.scratch_ml, error_word=ctx.error_word, chunk=chunk)
         return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
-                          partial_ok=True)
+                          partial_ok=self.partial_sums)
+
+    def _forward_wide(self, ctx, cache, batch, qkv, q, rotary) -> torch.Tensor:
+        """Norms over the whole projections, values of their own width, a sink and a gate per head: one kernel between
+        the product and attention, the generic attention kernel (32-bit arithmetic in both dtypes) with the sink in
+        its denominator and the gate in its last step, the output product."""
+        if rotary is not None and rotary.angles is not None:
+            raise NotImplementedError("angles computed per step are not built for this arrangement")
+        rows = q.shape[0]
+        gates = torch.empty((rows, self.n_q), dtype=torch.float32, device=q.device) if self.names.gate else None
+        ops.proj_norm_rope_kv(
+            qkv, q, cache.k_pool, cache.v_pool, ctx.positions, batch.slots if cache.writable else None,
+            self.q_norm if self.whole_norm else None, self.k_norm if self.whole_norm else None,
+            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, rotary.inv_freq if rotary else None,
+            rotary.rotary_dim if rotary else 0, rotary.interleaved if rotary else False, self.n_q, self.n_kv, self.d,
+            self.vd, ctx.error_word, magnitude=rotary.magnitude if rotary is not None else 1.0, gate_out=gates)
+        out = torch.empty((rows, self.n_q, self.vd), dtype=q.dtype, device=q.device)
+        for launch in batch.launches:
+            b, e = launch.begin, launch.end
+            ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e], ctx.row_request[b:e],
+                                batch.block_table, scale=self.scale, window=self.window or 0,
+                                split_size=launch.split_size, max_splits=launch.max_splits,
+                                scratch_acc=batch.scratch_acc, scratch_ml=batch.scratch_ml, error_word=ctx.error_word,
+                                chunk=self.chunk or 0, sinks=self.sinks, gates=None if gates is None else gates[b:e])
+        return ops.linear(out.view(rows, self.n_q * self.vd), self.w_o, self.b_o, error_word=ctx.error_word,
+                          partial_ok=self.partial_sums)

@@ -38,11 +38,17 @@ class TensorSpec:
 class PagedKV:
     """A mixer that keeps keys and values per token.  ``window`` None keeps all of them;
     a number keeps only what the last ``window`` positions can still see.  ``values`` False keeps one
-    row per token and kv head only (a latent that serves as key and as value): no value pool is made."""
+    row per token and kv head only (a latent that serves as key and as value): no value pool is made.
+    ``value_dim``: the width of a value row where it differs from the keys' ``head_dim`` (None: the same)."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    value_dim: Optional[int] = None
+
+    @property
+    def value_width(self) -> int:
+        return 0 if not self.values else (self.value_dim if self.value_dim is not None else self.head_dim)
 
 
 @dataclass(frozen=True)

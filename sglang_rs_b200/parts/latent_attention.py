@@ -24,6 +24,9 @@ Variations, each off unless asked for: queries straight from the input, q = W_q 
 a down-projection of its own (``names.kv_down`` None) that reads the latents another layer's cache holds, with its own
 W_uk, W_uv, queries and window: the model's program gives it that layer's cache, read-only (``LayerCall.cache_from``).
 ``cache_window`` is what the cache must keep (the widest window of all layers that read it; None: every row).
+The rotation may pair entry 2i with 2i + 1 (``rotary.interleaved``) and may stretch its long wavelengths and scale its
+cosines and sines (``rotary.scaling``); the gate may be one logit per entry of the joined heads instead of one per head
+(``gate_per_entry``: ``names.gate`` is then [heads * vdim, hidden]).
 """
 from __future__ import annotations
 
@@ -56,7 +59,7 @@ class LatentAttention(Mixer):
 
     def __init__(self, hidden: int, num_heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
                  scale: float, eps: float, rotary: Optional[RotaryEncoding], names: LatentAttentionNames, *,
-                 window: Optional[int] = None, cache_window: Optional[int] = -1):
+                 window: Optional[int] = None, cache_window: Optional[int] = -1, gate_per_entry: bool = False):
         """``rotary``: the rotation of the rot_dim part (its ``rotary_dim`` leading entries are rotated, the rest
         pass unchanged); None leaves it alone.  ``names.sink`` / ``names.gate`` None: no sink / no gate.
         ``cache_window`` -1: the layer's own window."""
@@ -78,8 +81,7 @@ class LatentAttention(Mixer):
             raise ValueError("latent attention: the cache keeps fewer rows than the layer sees")
         if rot_dim < 0 or (rotary is not None and rotary.rotary_dim > rot_dim):
             raise ValueError(f"latent attention: the rotation covers more than the {rot_dim} rotated entries")
-        if rotary is not None and rotary.interleaved:
-            raise ValueError("latent attention: only the half-split pairing of rotated entries is built")
+        self.gate_per_entry = bool(gate_per_entry)
         if kv_rank > 1024:
             raise ValueError(f"latent attention: a latent of {kv_rank} entries exceeds the 1024 the attention kernel takes")
         self.hidden, self.heads, self.dim, self.rot_dim, self.vdim = int(hidden), int(num_heads), int(dim), int(rot_dim), int(value_dim)
@@ -113,7 +115,7 @@ class LatentAttention(Mixer):
         if n.sink:
             specs[n.sink] = TensorSpec((h,))
         if n.gate:
-            specs[n.gate] = TensorSpec((h, self.hidden))
+            specs[n.gate] = TensorSpec((h * self.vdim if self.gate_per_entry else h, self.hidden))
         if self.rotary is not None:
             specs.update(self.rotary.tensor_specs())
         return specs
@@ -140,6 +142,7 @@ class LatentAttention(Mixer):
         rows, h = x.shape[0], self.heads
         rotary = self.rotary.fused_rotary() if self.rotary is not None else None
         inv_freq, rotary_dim = (rotary.inv_freq, rotary.rotary_dim) if rotary is not None else (None, 0)
+        turn = dict(interleaved=rotary.interleaved, magnitude=rotary.magnitude) if rotary is not None else {}
         proj = ops.linear(x, self.w_in, error_word=ctx.error_word)
         q_cols = self.q_rank or h * (self.dim + self.rot_dim)
         kv_cols = self.row_width if self.names.kv_down else 0
@@ -148,18 +151,19 @@ class LatentAttention(Mixer):
         if self.q_rank:
             ops.latent_prepare(proj, self.q_rank, self.kv_rank, self.rot_dim, self.q_norm, self.kv_norm, self.eps,
                                ctx.positions, inv_freq, rotary_dim, q_latent, cache.k_pool if stores else None,
-                               batch.slots if stores else None, ctx.error_word)
+                               batch.slots if stores else None, ctx.error_word, **turn)
             q = ops.linear(q_latent, self.w_uq, error_word=ctx.error_word).view(rows, h, self.dim + self.rot_dim)
         else:
             if stores:
                 ops.latent_prepare(proj[:, q_cols:], 0, self.kv_rank, self.rot_dim, None, self.kv_norm, self.eps,
-                                   ctx.positions, inv_freq, rotary_dim, None, cache.k_pool, batch.slots, ctx.error_word)
+                                   ctx.positions, inv_freq, rotary_dim, None, cache.k_pool, batch.slots, ctx.error_word,
+                                   **turn)
             q = proj[:, :q_cols].unflatten(1, (h, self.dim + self.rot_dim))
         # queries in the cache's own space: [W_uk^T q_plain | rotated part]
         q_row = torch.empty((rows, h, self.row_width), dtype=x.dtype, device=x.device)
         ops.head_linear(q, self.w_qk, q_row)
         if self.rot_dim:
-            ops.rope_slice(q, self.dim, q_row, self.kv_rank, self.rot_dim, rotary_dim, ctx.positions, inv_freq)
+            ops.rope_slice(q, self.dim, q_row, self.kv_rank, self.rot_dim, rotary_dim, ctx.positions, inv_freq, **turn)
         mixed = torch.empty((rows, h, self.kv_rank), dtype=x.dtype, device=x.device)
         tensor_cores = ops.latent_attention_takes(x.dtype, self.row_width, self.kv_rank)
         window = self.window or 0
@@ -183,5 +187,5 @@ class LatentAttention(Mixer):
                                 scratch_ml=batch.scratch_ml, error_word=ctx.error_word, sinks=self.sink)
         out = torch.empty((rows, h, self.vdim), dtype=x.dtype, device=x.device)
         gate = proj[:, q_cols + kv_cols:] if self.names.gate else None
-        ops.head_linear(mixed, self.w_uv, out, gate=gate)
+        ops.head_linear(mixed, self.w_uv, out, gate=gate, gate_per_entry=self.gate_per_entry)
         return ops.linear(out.view(rows, h * self.vdim), self.w_o, error_word=ctx.error_word)

@@ -3,6 +3,8 @@
 x <- W_in [x ; x0] + step[t]: the stream x is joined with the embedding output x0 (x first), mixed by one
 matrix [width, 2 width], and the pass's own vector step[t] (t = 0, 1, ...: the number of the pass) is added.
 The product's result and the sum are 32-bit: they become the residual stream.
+
+:class:`PassSum` is the head of a pass without tensors: x <- x + x0, the embedding output added to the stream, in 32-bit.
 """
 from __future__ import annotations
 
@@ -36,3 +38,16 @@ class PassEntry(Part):
         joined = torch.empty((residual.shape[0], 2 * self.width), dtype=ctx.dtype, device=residual.device)
         add_pending(residual, delta, None, joined, extra=origin)
         return ops.linear(joined, self.matrix, self.steps[pass_index], out_dtype=torch.float32, error_word=ctx.error_word)
+
+
+class PassSum(Part):
+    """x <- x + x0 at the head of a pass: the embedding output is added to the stream, once, right before the pass's
+    first layer.  The pending term of the layer before (with its norm, if it has one), this sum and the write of the
+    stream are one kernel; all 32-bit.  The stream is changed in place, so the model keeps the embedding output apart."""
+    graph_safe = True
+    #: the stream that ``forward`` returns is the one it was given
+    in_place = True
+
+    def forward(self, ctx, residual: torch.Tensor, delta, origin: torch.Tensor, pass_index: int) -> torch.Tensor:
+        add_pending(residual, delta, None, None, addend=origin)
+        return residual

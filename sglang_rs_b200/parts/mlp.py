@@ -28,10 +28,15 @@ class GatedMlpNames:
 class GatedMlp(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden: int, inner: int, activation: str, names: GatedMlpNames):
+    def __init__(self, hidden: int, inner: int, activation: str, names: GatedMlpNames, *, float_result: bool = False,
+                 partial_sums: bool = True):
+        """``float_result``: the second product keeps its 32-bit accumulator (for a consumer that adds it to other 32-bit
+        terms, as routed experts do with an expert that all rows share).  ``partial_sums`` False: the result is one
+        tensor, never partial sums along K (for a consumer that cannot add them)."""
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"unsupported activation {activation}; available: {sorted(ops.ACTIVATIONS)}")
         self.hidden, self.inner, self.activation, self.names = int(hidden), int(inner), activation, names
+        self.float_result, self.partial_sums = bool(float_result), bool(partial_sums)
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -47,7 +52,7 @@ class GatedMlp(FeedForward):
     def native_record(self):
         """This feed-forward for the step executor: the two stacked matrices, the inner width, the activation."""
         from ..ops.records import SxGatedMlp, linear_record
-        if self.w_gate_up is None:
+        if self.w_gate_up is None or self.float_result:
             return None
         return SxGatedMlp(linear_record(self.w_gate_up, None), linear_record(self.w_down, None), self.inner,
                           ops.activation_code(self.activation))
@@ -55,7 +60,9 @@ class GatedMlp(FeedForward):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         error_word = ctx.error_word if ctx is not None else None
         act = ops.gated_product(x, self.w_gate_up, self.inner, error_word, self.activation)
-        return ops.linear(act, self.w_down, error_word=error_word, partial_ok=True)
+        if self.float_result:
+            return ops.linear(act, self.w_down, out_dtype=torch.float32, error_word=error_word)
+        return ops.linear(act, self.w_down, error_word=error_word, partial_ok=self.partial_sums)
 
 
 class PlainMlp(FeedForward):

@@ -17,6 +17,9 @@ Scores may be the sigmoid of each logit instead of the softmax over all (``scori
 ``renormalize`` the chosen scores are divided by their sum plus ``norm_eps``; ``weight_scale`` multiplies the weights.
 An activation with a parameter (``swiglu_clamp``: g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit) and
 u' = clamp(u, -limit, limit)) takes it as ``activation_param``.
+``identity``: the router has this many outputs behind the experts' that stand for experts without tensors, whose result is
+their input: a row that chooses one gets weight * h as that term.  Scores, the correction and the choice run over all
+router outputs alike (the router matrix and the correction have experts + identity rows).
 """
 from __future__ import annotations
 
@@ -36,15 +39,18 @@ class RoutedExperts(FeedForward):
                  expert_names: Callable[[int], GatedMlpNames], renormalize: bool = False, *,
                  router_bias_name: Optional[str] = None, shared: Optional[FeedForward] = None,
                  scoring: str = "softmax", choice_bias_name: Optional[str] = None, weight_scale: float = 1.0,
-                 norm_eps: float = 0.0, activation_param: float = 0.0):
+                 norm_eps: float = 0.0, activation_param: float = 0.0, identity: int = 0):
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"unsupported activation {activation}; available: {sorted(ops.ACTIVATIONS)}")
         if scoring not in ops.ROUTER_SCORING:
             raise ValueError(f"unsupported scoring {scoring}; available: {sorted(ops.ROUTER_SCORING)}")
-        if not 0 < top <= experts:
-            raise ValueError(f"{top} chosen experts of {experts}")
-        if experts > 1024 or top > 32:
-            raise ValueError(f"the router kernel takes at most 1024 experts and 32 chosen ones, not {experts} and {top}")
+        if identity < 0:
+            raise ValueError(f"{identity} experts that return their input")
+        if not 0 < top <= experts + identity or experts <= 0:
+            raise ValueError(f"{top} chosen experts of {experts + identity}")
+        if experts + identity > 1024 or top > 32:
+            raise ValueError(f"the router kernel takes at most 1024 experts and 32 chosen ones, not {experts + identity} and {top}")
+        self.identity = int(identity)
         self.hidden, self.inner, self.experts, self.top = int(hidden), int(inner), int(experts), int(top)
         self.activation, self.router_name, self.renormalize = activation, router_name, bool(renormalize)
         self.names = [expert_names(e) for e in range(self.experts)]
@@ -57,11 +63,12 @@ class RoutedExperts(FeedForward):
         self.router = self.w_gate_up = self.w_down = self.router_bias = self.choice_bias = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        specs = {self.router_name: TensorSpec((self.experts, self.hidden))}
+        routes = self.experts + self.identity
+        specs = {self.router_name: TensorSpec((routes, self.hidden))}
         if self.router_bias_name:
-            specs[self.router_bias_name] = TensorSpec((self.experts,))
+            specs[self.router_bias_name] = TensorSpec((routes,))
         if self.choice_bias_name:
-            specs[self.choice_bias_name] = TensorSpec((self.experts,))
+            specs[self.choice_bias_name] = TensorSpec((routes,))
         if self.shared is not None:
             specs.update(self.shared.tensor_specs())
         for n in self.names:
@@ -93,4 +100,4 @@ class RoutedExperts(FeedForward):
                                   self.renormalize, ctx.error_word, gated=self.gated, router_bias=self.router_bias,
                                   base=base, scoring=self.scoring, choice_bias=self.choice_bias,
                                   weight_scale=self.weight_scale, norm_eps=self.norm_eps,
-                                  activation_param=self.activation_param)
+                                  activation_param=self.activation_param, identity=self.identity)

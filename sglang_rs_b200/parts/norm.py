@@ -50,23 +50,29 @@ class RmsNorm(Norm):
 class GroupedRmsNorm(Norm):
     """An RMS norm taken in ``groups`` equal consecutive parts of the row: each part is divided by its own
     sqrt(mean(part^2) + eps), then the whole row is multiplied by the weight and by ``scale`` (a constant, 1 unless a
-    design weighs the normed term in a residual sum).  With one group and scale 1 it is the plain RMS norm.  Like
+    design weighs the normed term in a residual sum).  With one group and scale 1 it is the plain RMS norm.
+    ``weight_offset``: the checkpoint stores the weight minus this number (1 for weights kept around zero: the row is
+    multiplied by 1 + w); the sum is taken once, at load, in 32-bit.  Like
     :class:`LayerNorm` it takes the pending term as a tensor or as a :class:`NormedDelta`, so a norm behind a sublayer,
     the residual sum and this norm run in one kernel; means, roots and the sum are 32-bit."""
     graph_safe = True
 
-    def __init__(self, width: int, eps: float, weight_name: str, groups: int = 1, scale: float = 1.0):
+    def __init__(self, width: int, eps: float, weight_name: str, groups: int = 1, scale: float = 1.0,
+                 weight_offset: float = 0.0):
         if groups < 1 or width % groups:
             raise ValueError(f"a row of {width} entries does not split into {groups} equal parts")
         self.width, self.eps, self.weight_name = int(width), float(eps), weight_name
-        self.groups, self.scale = int(groups), float(scale)
+        self.groups, self.scale, self.weight_offset = int(groups), float(scale), float(weight_offset)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {self.weight_name: TensorSpec((self.width,), "scale")}
+        # a weight stored minus an offset lies around zero
+        return {self.weight_name: TensorSpec((self.width,), "normal" if self.weight_offset else "scale")}
 
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.weight = scale_to(tensors[self.weight_name], device)
+        if self.weight_offset:
+            self.weight = self.weight + self.weight_offset
 
     def spec(self):
         return ("rms", self.weight, None, self.eps, self.groups, self.scale)
@@ -115,10 +121,11 @@ class LayerNorm(Norm):
 
 
 def add_pending(residual: torch.Tensor, delta, outer, out: Optional[torch.Tensor],
-                row_index: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None) -> None:
-    """residual += delta (a tensor, a :class:`NormedDelta` or None), then ``out`` = ``outer`` of the sum."""
+                row_index: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+                addend: Optional[torch.Tensor] = None) -> None:
+    """residual += delta (a tensor, a :class:`NormedDelta` or None) (+ ``addend``), then ``out`` = ``outer`` of the sum."""
     inner = None
     if isinstance(delta, NormedDelta):
         inner, delta = delta.norm.spec(), delta.values
     ops.norm_add_norm(residual, delta, inner, outer, out, row_index=row_index, write_residual=row_index is None,
-                      extra=extra)
+                      extra=extra, addend=addend)
