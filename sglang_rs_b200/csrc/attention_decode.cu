@@ -306,8 +306,18 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           l += ls[b] * weight;
         }
       }
-      out[((size_t)row * p.n_q + (size_t)kv_head * groups + head) * D + e] =
-          __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+      const int q_head = kv_head * groups + head;
+      if (p.sinks) {
+        // the sink joins the denominator here, where all blocks' parts meet: once per row
+        const float sink = p.sinks[q_head] * 1.4426950408889634f;
+        const float m_all = fmaxf(m, sink);
+        const float shrink = exp2f(m - m_all);
+        acc *= shrink;
+        l = l * shrink + exp2f(sink - m_all);
+      }
+      float result = l > 0.f ? acc / l : 0.f;
+      if (p.gates) result *= p.gates[(size_t)row * p.n_q + q_head];
+      out[((size_t)row * p.n_q + q_head) * D + e] = __float2bfloat16_rn(result);
     }
     srb_cluster_sync();                                    // nobody leaves while its memory may still be read
     srb_mark(SRB_MARK_DECODE_ATTENTION, 2);
@@ -336,17 +346,22 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const size_t first = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits;
     // lane s holds split s (and s + 32, ...): maxima and sums go through the fixed butterfly of the warp,
     // so their order does not depend on which block merges
+    const int q_head = kv_head * groups + head;
     float m = -INFINITY;
     for (int sp = lane; sp < count; sp += 32) m = fmaxf(m, __ldcg(part_ml + (first + sp) * 2));
     m = srb_warp_max(m);
+    // the sink joins the denominator here, where all splits meet: once per row
+    const float sink = p.sinks ? p.sinks[q_head] * 1.4426950408889634f : -INFINITY;
+    m = fmaxf(m, sink);
     float lw = 0.f;
     for (int sp = lane; sp < count; sp += 32) {
       const float w = exp2f(__ldcg(part_ml + (first + sp) * 2) - m);
       lw += __ldcg(part_ml + (first + sp) * 2 + 1) * w;
       weights[head * (count + 1) + sp] = w;
     }
-    const float l = srb_warp_sum(lw);
-    if (lane == 0) weights[head * (count + 1) + count] = 1.0f / l;
+    float l = srb_warp_sum(lw);
+    if (p.sinks) l += exp2f(sink - m);
+    if (lane == 0) weights[head * (count + 1) + count] = (p.gates ? p.gates[(size_t)row * p.n_q + q_head] : 1.0f) / l;
   }
   __syncthreads();
   // four (head, element) pairs per thread and eight splits at a time: 32 loads in flight, added in split order
@@ -419,11 +434,14 @@ extern "C" int srb_decode_attention_supports(int n_q, int n_kv, int head_dim, in
 // rows * n_q * num_splits * head_dim floats, part_ml rows * n_q * num_splits * 2; `counters` holds
 // rows * n_kv ints that are zero before the call and zero again after it.
 // `chunk` > 0: a row sees only the keys of its own chunk of positions, counted from position 0.
-extern "C" int srb_decode_attention_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                           float* part_acc, float* part_ml, int* counters, const int* positions,
-                                           const int* row_request, const int* block_table, int table_stride, int rows,
-                                           int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
-                                           int chunk, int num_splits, float scale, int* error_word, void* stream) {
+// `sinks` (float [n_q], or null): exp(sink_h) joins the softmax's denominator of head h, once per row; `gates` (float
+// [rows, n_q], or null): a factor on the result of every (row, query head).
+extern "C" int srb_decode_attention_gated(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                          float* part_acc, float* part_ml, int* counters, const int* positions,
+                                          const int* row_request, const int* block_table, int table_stride, int rows,
+                                          int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                          int chunk, int num_splits, float scale, int* error_word, const float* sinks,
+                                          const float* gates, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (chunk < 0) SRB_FAIL("decode_attention: the chunk size must be non-negative");
   if (!srb_decode_attention_supports(n_q, n_kv, head_dim, SRB_DTYPE_BF16))
@@ -438,11 +456,21 @@ extern "C" int srb_decode_attention_masked(const void* q, const void* k_pool, co
   p.positions = positions; p.row_request = row_request; p.block_table = block_table;
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
   p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.split_size = 0;
-  p.max_splits = num_splits; p.scale = scale; p.error_word = error_word;
+  p.max_splits = num_splits; p.scale = scale; p.error_word = error_word; p.sinks = sinks; p.gates = gates;
   dp.scale_log2 = scale * 1.4426950408889634f;
   cudaStream_t s = (cudaStream_t)stream;
   if (head_dim == 64) return launch_decode<64>(q, k_pool, v_pool, out, part_acc, part_ml, counters, dp, rows, s);
   return launch_decode<128>(q, k_pool, v_pool, out, part_acc, part_ml, counters, dp, rows, s);
+}
+
+extern "C" int srb_decode_attention_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           float* part_acc, float* part_ml, int* counters, const int* positions,
+                                           const int* row_request, const int* block_table, int table_stride, int rows,
+                                           int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                           int chunk, int num_splits, float scale, int* error_word, void* stream) {
+  return srb_decode_attention_gated(q, k_pool, v_pool, out, part_acc, part_ml, counters, positions, row_request, block_table,
+                                    table_stride, rows, n_q, n_kv, head_dim, page_size, num_pages, window, chunk, num_splits,
+                                    scale, error_word, nullptr, nullptr, stream);
 }
 
 extern "C" int srb_decode_attention(const void* q, const void* k_pool, const void* v_pool, void* out,

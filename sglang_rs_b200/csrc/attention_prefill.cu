@@ -226,7 +226,16 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (r_in[h] >= n_rows) continue;
-    const float inv = 1.0f / l_row[h];
+    float l_all = l_row[h], shrink = 1.f;
+    if (p.sinks) {
+      // the sink is one more term of the denominator: 2^(sink log2 e - M) with M the larger of the two maxima
+      const float sink = p.sinks[head] * 1.4426950408889634f;
+      const float m_all = fmaxf(m_row[h], sink);
+      shrink = exp2f(m_row[h] - m_all);
+      l_all = l_all * shrink + exp2f(sink - m_all);
+    }
+    float inv = shrink / l_all;
+    if (p.gates) inv *= p.gates[(size_t)(row_begin + r_in[h]) * p.n_q + head];
     __nv_bfloat16* dst = out + ((size_t)(row_begin + r_in[h]) * p.n_q + head) * D;
 #pragma unroll
     for (int t = 0; t < NT_O; ++t)
@@ -257,10 +266,13 @@ extern "C" int srb_prefill_tile_rows() { return PF_ROWS; }
 
 // q, out: [rows, n_q, head_dim] of the whole step; tiles: [num_tiles, 4] ints (see the top).
 // `chunk` > 0: a row sees only the keys of its own chunk of positions, counted from position 0.
-extern "C" int srb_prefill_attention_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                            const int* tiles, int num_tiles, const int* block_table, int table_stride,
-                                            int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
-                                            int chunk, float scale, int* error_word, void* stream) {
+// `sinks` (float [n_q], or null): exp(sink_h) joins the softmax's denominator of head h; `gates` (float [rows, n_q], or
+// null): a factor on the result of every (row, query head).
+extern "C" int srb_prefill_attention_gated(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                           const int* tiles, int num_tiles, const int* block_table, int table_stride,
+                                           int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                           int chunk, float scale, int* error_word, const float* sinks, const float* gates,
+                                           void* stream) {
   if (num_tiles <= 0) return SRB_OK;
   if (chunk < 0) SRB_FAIL("prefill_attention: the chunk size must be non-negative");
   if (!srb_prefill_attention_supports(n_q, n_kv, head_dim, SRB_DTYPE_BF16))
@@ -272,10 +284,18 @@ extern "C" int srb_prefill_attention_masked(const void* q, const void* k_pool, c
   p.positions = nullptr; p.row_request = nullptr; p.block_table = block_table;
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;
   p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.chunk = chunk; p.split_size = 0;
-  p.max_splits = 1; p.scale = scale; p.error_word = error_word;
+  p.max_splits = 1; p.scale = scale; p.error_word = error_word; p.sinks = sinks; p.gates = gates;
   cudaStream_t s = (cudaStream_t)stream;
   if (head_dim == 64) return launch_prefill<64>(q, k_pool, v_pool, out, tiles, num_tiles, p, s);
   return launch_prefill<128>(q, k_pool, v_pool, out, tiles, num_tiles, p, s);
+}
+
+extern "C" int srb_prefill_attention_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                            const int* tiles, int num_tiles, const int* block_table, int table_stride,
+                                            int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
+                                            int chunk, float scale, int* error_word, void* stream) {
+  return srb_prefill_attention_gated(q, k_pool, v_pool, out, tiles, num_tiles, block_table, table_stride, n_q, n_kv, head_dim,
+                                     page_size, num_pages, window, chunk, scale, error_word, nullptr, nullptr, stream);
 }
 
 extern "C" int srb_prefill_attention(const void* q, const void* k_pool, const void* v_pool, void* out,

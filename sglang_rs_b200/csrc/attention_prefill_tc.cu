@@ -43,6 +43,8 @@ struct TcArgs {
   int table_stride, n_q, n_kv, page_size, pool_rows, window, chunk;
   float scale_log2;
   int* error_word;
+  const float* sinks;      // [n_q] or null: exp(sink_h) joins the softmax's denominator of head h, once per row
+  const float* gates;      // [rows, n_q] or null: a factor on the result of every (row, query head)
 };
 
 // M = 128, N = n, A and B bfloat16, D float; b_mn_major: B is [K rows][N contiguous] (V), else K-major
@@ -382,7 +384,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     unsigned char* stage = q_smem + t * Q_BYTES;
     if (ok) {
       tc_fence_after();
-      const float inv = row_live && l_run > 0.f ? 1.0f / l_run : 0.f;
+      float l_all = l_run, shrink = 1.f;
+      if (args.sinks && row_live) {
+        // the sink is one more term of the denominator: 2^(sink log2 e - M) with M the larger of the two maxima
+        const float sink = args.sinks[head] * 1.4426950408889634f;
+        const float m_all = fmaxf(m_run, sink);
+        shrink = ex2(m_run - m_all);
+        l_all = l_run * shrink + ex2(sink - m_all);
+      }
+      float inv = row_live && l_all > 0.f ? shrink / l_all : 0.f;
+      if (args.gates && row_live) inv *= args.gates[(size_t)(row_begin + r) * args.n_q + head];
       __nv_bfloat16* dst = args.out + ((size_t)(row_begin + r) * args.n_q + head) * D;
 #pragma unroll 2
       for (int c = 0; c < D; c += 32) {
@@ -477,11 +488,13 @@ static int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const C
 // q, out: [rows, n_q, head_dim] bfloat16 of the whole step; pools [pages, n_kv, page_size, head_dim];
 // tiles: [num_tiles, 4] ints with at most 128 rows each.
 // `chunk` > 0: a row sees only the keys of its own chunk of positions, counted from position 0.
-extern "C" int srb_prefill_attention_tc_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                               const int* tiles, int num_tiles, int rows, const int* block_table,
-                                               int table_stride, int n_q, int n_kv, int head_dim, int page_size,
-                                               int num_pages, int window, int chunk, float scale, int* error_word,
-                                               void* stream) {
+// `sinks` (float [n_q], or null): exp(sink_h) joins the softmax's denominator of head h; `gates` (float [rows, n_q], or
+// null): a factor on the result of every (row, query head).
+extern "C" int srb_prefill_attention_tc_gated(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                              const int* tiles, int num_tiles, int rows, const int* block_table,
+                                              int table_stride, int n_q, int n_kv, int head_dim, int page_size,
+                                              int num_pages, int window, int chunk, float scale, int* error_word,
+                                              const float* sinks, const float* gates, void* stream) {
   if (num_tiles <= 0) return SRB_OK;
   if (chunk < 0) SRB_FAIL("prefill_attention_tc: the chunk size must be non-negative");
   if (!srb_prefill_tc_supports(n_q, n_kv, head_dim, page_size, SRB_DTYPE_BF16))
@@ -522,6 +535,7 @@ extern "C" int srb_prefill_attention_tc_masked(const void* q, const void* k_pool
   args.tiles = tiles; args.block_table = block_table; args.out = (__nv_bfloat16*)out; args.table_stride = table_stride;
   args.n_q = n_q; args.n_kv = n_kv; args.page_size = page_size; args.pool_rows = (int)pool_rows; args.window = window; args.chunk = chunk;
   args.scale_log2 = scale * 1.4426950408889634f; args.error_word = error_word;
+  args.sinks = sinks; args.gates = gates;
   cudaStream_t s = (cudaStream_t)stream;
   // two query heads per block when the heads of a kv head pair up
   const bool pairs = (n_q / n_kv) % 2 == 0;
@@ -530,6 +544,16 @@ extern "C" int srb_prefill_attention_tc_masked(const void* q, const void* k_pool
                  : launch_tc<64, 1, 2>(map_q, map_k, map_v, map_out, args, num_tiles, s);
   return pairs ? launch_tc<128, 2, 4>(map_q, map_k, map_v, map_out, args, num_tiles, s)
                : launch_tc<128, 1, 2>(map_q, map_k, map_v, map_out, args, num_tiles, s);
+}
+
+extern "C" int srb_prefill_attention_tc_masked(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                               const int* tiles, int num_tiles, int rows, const int* block_table,
+                                               int table_stride, int n_q, int n_kv, int head_dim, int page_size,
+                                               int num_pages, int window, int chunk, float scale, int* error_word,
+                                               void* stream) {
+  return srb_prefill_attention_tc_gated(q, k_pool, v_pool, out, tiles, num_tiles, rows, block_table, table_stride, n_q, n_kv,
+                                        head_dim, page_size, num_pages, window, chunk, scale, error_word, nullptr, nullptr,
+                                        stream);
 }
 
 extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out,

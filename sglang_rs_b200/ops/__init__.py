@@ -600,9 +600,9 @@ def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                      scale: float, window: int, scratch_acc: torch.Tensor, scratch_ml: torch.Tensor,
                      counters: torch.Tensor, error_word: torch.Tensor, max_keys: Optional[int] = None,
-                     chunk: int = 0) -> None:
-    """Attention of decoded tokens (one row each), bfloat16, head_dim 64 or 128; ``window`` and ``chunk`` as in
-    :func:`paged_attention`.
+                     chunk: int = 0, sinks: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None) -> None:
+    """Attention of decoded tokens (one row each), bfloat16, head_dim 64 or 128; ``window``, ``chunk``, ``sinks`` and
+    ``gates`` as in :func:`paged_attention` (the sink joins where a row's splits are merged, once).
 
     The keys of a (row, kv head) are shared by ``decode_splits(rows, n_kv, max_keys)`` blocks
     (``max_keys``: the most keys any row sees, if known); the block that finishes last merges them.  ``counters``: int32, zero, at least rows * n_kv entries; they
@@ -624,11 +624,21 @@ def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         raise KernelError("decode_attention: scratch tensors are too small")
     if counters.numel() < rows * n_kv:
         raise KernelError("decode_attention: too few counters")
+    rows_, heads_ = q.shape[0], q.shape[1]
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32)
+        if sinks.numel() != heads_:
+            raise KernelError("decode_attention: one sink per query head is needed")
+    if gates is not None:
+        _need(gates, "gates", torch.float32)
+        if gates.shape != (rows_, heads_):
+            raise KernelError("decode_attention: one gate per row and query head is needed")
     lib = load_library("attention_decode")
-    _check(lib, lib.srb_decode_attention_masked(
+    _check(lib, lib.srb_decode_attention_gated(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(counters),
         _ptr(positions), _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim,
-        page_size, num_pages, int(window), int(chunk), splits, ctypes.c_float(scale), _ptr(error_word), _stream()))
+        page_size, num_pages, int(window), int(chunk), splits, ctypes.c_float(scale), _ptr(error_word), _ptr(sinks),
+        _ptr(gates), _stream()))
 
 
 def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
@@ -641,8 +651,9 @@ def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int
 @traced("attention_prefill")
 def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                     tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
-                    error_word: torch.Tensor, chunk: int = 0) -> None:
-    """Attention of prompt portions, bfloat16.  ``tiles`` is int32 [n, 4]: first row of the
+                    error_word: torch.Tensor, chunk: int = 0, sinks: Optional[torch.Tensor] = None,
+                    gates: Optional[torch.Tensor] = None) -> None:
+    """Attention of prompt portions, bfloat16 (``sinks``, ``gates``: as in :func:`paged_attention`).  ``tiles`` is int32 [n, 4]: first row of the
     step, rows (at most 64, consecutive rows of one request), request index, first position.
     Rows outside the tiles are left untouched."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
@@ -652,11 +663,20 @@ def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     num_pages, n_kv, page_size, pool_dim = k_pool.shape
     if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape or tiles.shape[-1] != 4:
         raise KernelError("tiled_attention: shapes of q, out, the pools and the tiles do not agree")
+    rows_, heads_ = q.shape[0], q.shape[1]
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32)
+        if sinks.numel() != heads_:
+            raise KernelError("tiled_attention: one sink per query head is needed")
+    if gates is not None:
+        _need(gates, "gates", torch.float32)
+        if gates.shape != (rows_, heads_):
+            raise KernelError("tiled_attention: one gate per row and query head is needed")
     lib = load_library("attention_prefill")
-    _check(lib, lib.srb_prefill_attention_masked(
+    _check(lib, lib.srb_prefill_attention_gated(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], _ptr(block_table),
         block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), int(chunk), ctypes.c_float(scale),
-        _ptr(error_word), _stream()))
+        _ptr(error_word), _ptr(sinks), _ptr(gates), _stream()))
 
 
 TC_TILE_ROWS = 128
@@ -672,9 +692,10 @@ def tiled_attention_tc_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: 
 @traced("attention_prefill")
 def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                        tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
-                       error_word: torch.Tensor, chunk: int = 0) -> None:
+                       error_word: torch.Tensor, chunk: int = 0, sinks: Optional[torch.Tensor] = None,
+                       gates: Optional[torch.Tensor] = None) -> None:
     """Attention of prompt portions on tcgen05 tensor cores (S, P and O in tensor memory, operands
-    by TMA).  ``tiles`` as for :func:`tiled_attention`, with at most 128 rows per tile."""
+    by TMA; ``sinks``, ``gates``: as in :func:`paged_attention`).  ``tiles`` as for :func:`tiled_attention`, with at most 128 rows per tile."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
     _need(v_pool, "v_pool", torch.bfloat16); _need(tiles, "tiles", torch.int32)
     _need(block_table, "block_table", torch.int32)
@@ -682,11 +703,20 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     num_pages, n_kv, page_size, pool_dim = k_pool.shape
     if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape or tiles.shape[-1] != 4:
         raise KernelError("tiled_attention_tc: shapes of q, out, the pools and the tiles do not agree")
+    rows_, heads_ = q.shape[0], q.shape[1]
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32)
+        if sinks.numel() != heads_:
+            raise KernelError("tiled_attention_tc: one sink per query head is needed")
+    if gates is not None:
+        _need(gates, "gates", torch.float32)
+        if gates.shape != (rows_, heads_):
+            raise KernelError("tiled_attention_tc: one gate per row and query head is needed")
     lib = load_library("attention_prefill_tc")
-    _check(lib, lib.srb_prefill_attention_tc_masked(
+    _check(lib, lib.srb_prefill_attention_tc_gated(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], rows, _ptr(block_table),
         block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), int(chunk), ctypes.c_float(scale),
-        _ptr(error_word), _stream()))
+        _ptr(error_word), _ptr(sinks), _ptr(gates), _stream()))
 
 
 # --------------------------------------------------------------------------- latents and per-head products

@@ -22,7 +22,8 @@ that width).  ``sink``: a number that joins the softmax's denominator as exp(sin
 every head (0 adds one to the denominator); it has no key and no value.  ``names.gate``: a matrix [n_q, hidden] whose
 product with the mixer's input gives a logit per head; head h's result is multiplied by its sigmoid before the output
 projection (the matrix rides in the q/k/v product, the factor in the attention kernel's last step).  A mixer with any of
-these runs ``ops.proj_norm_rope_kv`` and the generic attention kernel, which carry them.
+these runs ``ops.proj_norm_rope_kv`` between the product and attention; every attention kernel takes the sink and the
+gates, and the tensor-core ones serve where values are as wide as the keys.
 """
 from __future__ import annotations
 
@@ -83,7 +84,7 @@ class GroupedQueryAttention(Mixer):
             raise ValueError(f"values of {self.vd} entries are outside what the attention kernels take (1 to 1024)")
         #: whether the output product may hand on partial sums along K (a consumer that cannot add them says no)
         self.partial_sums = bool(partial_sums)
-        #: the arrangement that only ``ops.proj_norm_rope_kv`` and the generic attention kernel carry
+        #: the arrangement that ``ops.proj_norm_rope_kv`` prepares
         self.wide = self.whole_norm or self.vd != self.d or self.sink is not None or names.gate is not None
         if self.wide and (self.values_from_keys or names.q_bias or names.k_bias or names.v_bias):
             raise ValueError("norms over whole projections, values of their own width, a sink and a gate are not built "
@@ -174,39 +175,50 @@ class GroupedQueryAttention(Mixer):
             angles=rotary.angles(ctx.positions) if rotary is not None and rotary.angles is not None else None,
             magnitude=rotary.magnitude if rotary is not None else 1.0, values_from_keys=self.values_from_keys)
         out = torch.empty_like(q)
-        chunk = self.chunk or 0
+        self._attend(ctx, cache, batch, q, out, None)
+        return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
+                          partial_ok=self.partial_sums)
+
+    def _attend(self, ctx, cache, batch, q, out, gates) -> None:
+        """The step's attention launches: the tensor-core kernels where they take the sizes (values as wide as the keys,
+        heads of 64 or 128), the generic kernel elsewhere; the sink and the gates go to whichever runs."""
+        chunk, sinks = self.chunk or 0, self.sinks
+        same_width = self.vd == self.d
         for launch in batch.launches:
             b, e = launch.begin, launch.end
-            if launch.wide_tiles is not None and ops.tiled_attention_tc_takes(q.dtype, self.n_q, self.n_kv, self.d,
-                                                                              cache.k_pool.shape[2]):
+            if same_width and launch.wide_tiles is not None and ops.tiled_attention_tc_takes(
+                    q.dtype, self.n_q, self.n_kv, self.d, cache.k_pool.shape[2]):
                 ops.tiled_attention_tc(q, cache.k_pool, cache.v_pool, out, launch.wide_tiles, batch.block_table,
-                                       scale=self.scale, window=self.window or 0, error_word=ctx.error_word, chunk=chunk)
+                                       scale=self.scale, window=self.window or 0, error_word=ctx.error_word, chunk=chunk,
+                                       sinks=sinks, gates=gates)
                 continue
-            if launch.tiles is not None and ops.tiled_attention_takes(q.dtype, self.n_q, self.n_kv, self.d):
+            if same_width and launch.tiles is not None and ops.tiled_attention_takes(q.dtype, self.n_q, self.n_kv, self.d):
                 ops.tiled_attention(q, cache.k_pool, cache.v_pool, out, launch.tiles, batch.block_table,
-                                    scale=self.scale, window=self.window or 0, error_word=ctx.error_word, chunk=chunk)
+                                    scale=self.scale, window=self.window or 0, error_word=ctx.error_word, chunk=chunk,
+                                    sinks=sinks, gates=gates)
                 continue
-            if (launch.tiles is None and launch.split_size and batch.counters is not None
+            row_gates = None if gates is None else gates[b:e]
+            if (same_width and launch.tiles is None and launch.split_size and batch.counters is not None
                     and batch.counters.numel() >= (e - b) * self.n_kv
                     and ops.decode_attention_takes(q.dtype, self.n_q, self.n_kv, self.d)):
                 ops.decode_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
                                      ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                      window=self.window or 0, scratch_acc=batch.scratch_acc,
                                      scratch_ml=batch.scratch_ml, counters=batch.counters,
-                                     error_word=ctx.error_word, max_keys=launch.max_keys, chunk=chunk)
+                                     error_word=ctx.error_word, max_keys=launch.max_keys, chunk=chunk, sinks=sinks,
+                                     gates=row_gates)
                 continue
             ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
                                 ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                 window=self.window or 0, split_size=launch.split_size,
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
-                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word, chunk=chunk)
-        return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
-                          partial_ok=self.partial_sums)
+                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word, chunk=chunk, sinks=sinks,
+                                gates=row_gates)
 
     def _forward_wide(self, ctx, cache, batch, qkv, q, rotary) -> torch.Tensor:
         """Norms over the whole projections, values of their own width, a sink and a gate per head: one kernel between
-        the product and attention, the generic attention kernel (32-bit arithmetic in both dtypes) with the sink in
-        its denominator and the gate in its last step, the output product."""
+        the product and attention, the attention kernels with the sink in the denominator and the gate in their last
+        step, the output product."""
         if rotary is not None and rotary.angles is not None:
             raise NotImplementedError("angles computed per step are not built for this arrangement")
         rows = q.shape[0]
@@ -218,12 +230,6 @@ class GroupedQueryAttention(Mixer):
             rotary.rotary_dim if rotary else 0, rotary.interleaved if rotary else False, self.n_q, self.n_kv, self.d,
             self.vd, ctx.error_word, magnitude=rotary.magnitude if rotary is not None else 1.0, gate_out=gates)
         out = torch.empty((rows, self.n_q, self.vd), dtype=q.dtype, device=q.device)
-        for launch in batch.launches:
-            b, e = launch.begin, launch.end
-            ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e], ctx.row_request[b:e],
-                                batch.block_table, scale=self.scale, window=self.window or 0,
-                                split_size=launch.split_size, max_splits=launch.max_splits,
-                                scratch_acc=batch.scratch_acc, scratch_ml=batch.scratch_ml, error_word=ctx.error_word,
-                                chunk=self.chunk or 0, sinks=self.sinks, gates=None if gates is None else gates[b:e])
+        self._attend(ctx, cache, batch, q, out, gates)
         return ops.linear(out.view(rows, self.n_q * self.vd), self.w_o, self.b_o, error_word=ctx.error_word,
                           partial_ok=self.partial_sums)

@@ -48,8 +48,8 @@ def frequencies(rot):
 
 
 def rotate(v, positions, rot, interleaved):
-    """v [tokens, heads, n]: the first rot.dims entries of each head are rotated, the rest pass."""
-    dims = int(rot["dims"])
+    """v [tokens, heads, n]: the first rot.dims entries of each head are rotated, the rest pass; no ``rot``, no rotation."""
+    dims = int(rot["dims"]) if rot else 0
     if dims == 0:
         return v
     f, mag = frequencies(rot)
@@ -90,8 +90,8 @@ def windowed_attention(h, positions, w, p, m, eps):
     q = rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]
     k = rms(h @ w[p + "k"].T, eps) * w[p + "k.norm"]
     v = (h @ w[p + "v"].T).reshape(T, G, dv)
-    q = rotate(q.reshape(T, H, d), positions, m["rot"], False)
-    k = rotate(k.reshape(T, G, d), positions, m["rot"], False)
+    q = rotate(q.reshape(T, H, d), positions, m.get("rot"), False)
+    k = rotate(k.reshape(T, G, d), positions, m.get("rot"), False)
     per = H // G
     kq = np.repeat(k, per, axis=1)
     vq = np.repeat(v, per, axis=1)
@@ -110,8 +110,8 @@ def latent_attention(h, positions, w, p, m, eps):
     q = (cq @ w[p + "uq"].T).reshape(T, H, d + r)
     down = h @ w[p + "dkv"].T
     c = rms(down[:, :rank], eps) * w[p + "dkv.norm"]
-    k_rot = rotate(down[:, None, rank:], positions, m["rot"], True)               # [T, 1, r]
-    q_rot = rotate(q[:, :, d:], positions, m["rot"], True)
+    k_rot = rotate(down[:, None, rank:], positions, m.get("rot"), True)               # [T, 1, r]
+    q_rot = rotate(q[:, :, d:], positions, m.get("rot"), True)
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, d)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     qq = np.concatenate([q[:, :, :d], q_rot], axis=2)
