@@ -159,7 +159,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel", "tosivik", "desarax"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline", "gegepel", "tosivik", "desarax", "titatar"))
     parser.add_argument("--rows", default="1,8,64,2048", help="--mode compare-cublas: the row counts, comma-separated")
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
@@ -191,6 +191,8 @@ def main() -> int:
         return tosivik_beside_qwen3(args, warmup)
     if args.mode == "desarax":
         return desarax_beside_tosivik(args, warmup)
+    if args.mode == "titatar":
+        return titatar_beside_gegepel(args, warmup)
 
     if args.mode == "timeline":
         # the kernels of a decode step, built with marks that record when each block starts, stops waiting for the
@@ -905,6 +907,41 @@ def desarax_beside_tosivik(args, warmup) -> int:
     note = {"layers": layers, "width": args.width, "vocab": vocab, "desarax_layers": designs["desarax"]["layers"][:4],
             "tosivik_layers": designs["tosivik"]["layers"][:4]}
     return designs_side_by_side(args, warmup, "desarax", designs, vocab, note)
+
+
+def titatar_layers(count: int):
+    """Layers of a real model's size at the width of ``--mode gegepel``: attention with 16 heads of 128 entries on 4 kv heads,
+    half of each head rotated, a window of 1,024 positions; attention through latents of that mode's sizes with stretched
+    wavelengths; a dense feed-forward of three widths in the first layer, then 64 experts of 1,408 with 6 chosen among
+    them and 8 router outputs without tensors, beside a shared expert of 2,816."""
+    windowed = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 1.0 / math.sqrt(128), "mask": {"size": 1024},
+                "rot": {"base": 1000000.0, "dims": 64}}
+    through_latents = {**GEGEPEL_MIXER, "rot": {"base": 10000.0, "dims": 64,
+                                                "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    experts = {"kind": "moe", "router": {"experts": 64, "top": 6, "identity": 8}, "expert": {"ff": 1408}, "shared": {"ff": 2816}}
+    pattern = [("attention", windowed, {"kind": "dense", "ff": 3 * GEGEPEL_WIDTH}), ("attention", windowed, experts),
+               ("latent_attention", through_latents, experts), ("latent_attention", through_latents, experts)]
+    return [{"type": kind, "mixer": mixer, "mlp": mlp} for kind, mixer, mlp in (pattern[i % 4] for i in range(count))]
+
+
+def titatar_beside_gegepel(args, warmup) -> int:
+    """``--mode titatar``: prefill and decode of a Titatar model with layers of a real model's size (random weights) beside
+    the Gegepel model of ``--mode gegepel`` (the closest design: attention through latents, routed experts, a stretch of
+    layers walked twice, a norm on both sides of every sublayer), at equal width, depth and layer runs."""
+    layers = args.layers if args.layers is not None else 4
+    vocab = 32768
+    loop = {"start": 1, "stop": min(3, layers), "times": 2} if layers >= 2 else None
+    block = {"type": "latent_attention", "mixer": GEGEPEL_MIXER, "mlp": GEGEPEL_MLP}
+    designs = {
+        "titatar": {"architecture": "Titatar", "vocab": vocab, "width": GEGEPEL_WIDTH, "embedding": {"scale": 1.0},
+                    "norm": {"eps": 1e-5}, "layers": titatar_layers(layers), "loop": loop},
+        "gegepel": {"architecture": "Gegepel", "vocab": vocab, "width": GEGEPEL_WIDTH, "embedding": {"scale": 1.0},
+                    "norm": {"eps": 1e-5}, "layers": [block] * layers, "loop": loop},
+    }
+    runs = layers + (min(3, layers) - 1 if layers >= 2 else 0)
+    note = {"layers": layers, "width": GEGEPEL_WIDTH, "vocab": vocab, "titatar_layers": designs["titatar"]["layers"][:4],
+            "gegepel_mixer": GEGEPEL_MIXER, "gegepel_mlp": GEGEPEL_MLP, "layer_runs": {"titatar": runs, "gegepel": runs}}
+    return designs_side_by_side(args, warmup, "titatar", designs, vocab, note)
 
 
 def designs_side_by_side(args, warmup, mode, designs, vocab, note) -> int:

@@ -649,8 +649,23 @@ extern "C" int srb_qk_norm_rope_kv_ex(const void* qkv, const float* qkv_parts, i
 // 32-bit, to `gate_out` [rows, gate_cols] for the attention kernel that multiplies its result by them.
 // Row of the projection: [n_q * head_dim | n_kv * head_dim | n_kv * value_dim | gate_cols].
 // One block per row; sums of squares, norms, angles and the rotation are 32-bit; a norm whose weight is null is left out.
-template <typename T>
-__global__ void __launch_bounds__(256)
+// Sum of two values over a block of up to 1024 threads at once; every thread receives both.  Warp partials are added in
+// warp order, so the results do not depend on timing.
+__device__ __forceinline__ float2 block_sum_pair(float a, float b, float* scratch /* >= 66 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  a = srb_warp_sum(a);
+  b = srb_warp_sum(b);
+  if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; }
+  __syncthreads();
+  float ta = 0.f, tb = 0.f;
+  for (int w = 0; w < warps; ++w) { ta += scratch[w]; tb += scratch[32 + w]; }
+  return make_float2(ta, tb);
+}
+
+// EIGHT: every width of the row's parts is a multiple of eight and all rows start on 16-byte borders, so a thread moves
+// eight consecutive entries at a time (16 bytes of bfloat16, two 16-byte pieces of float), never across a head's end.
+template <typename T, bool EIGHT>
+__global__ void __launch_bounds__(512)
 proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_parts, int num_parts, size_t part_stride,
                          int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool,
                          float* __restrict__ gate_out, const int* __restrict__ positions, const int* __restrict__ slots,
@@ -658,9 +673,10 @@ proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qk
                          const float* __restrict__ inv_freq, int rotary_dim, int interleaved, float magnitude, int n_q,
                          int n_kv, int head_dim, int value_dim, int gate_cols, int page_size, int num_pages,
                          int* error_word) {
-  extern __shared__ __align__(16) float staged[];       // (n_q + n_kv) * head_dim values, rotary_dim cosines and sines, 33 of scratch
-  const int q_width = n_q * head_dim, k_width = n_kv * head_dim;
-  float* cos_table = staged + q_width + k_width;
+  extern __shared__ __align__(16) float staged[];       // the row (q, k, v, gate logits), rotary_dim cosines and sines, 66 of scratch
+  const int q_width = n_q * head_dim, k_width = n_kv * head_dim, v_width = n_kv * value_dim;
+  const int row_width = q_width + k_width + v_width + gate_cols;
+  float* cos_table = staged + ((row_width + 3) & ~3);
   float* sin_table = cos_table + (rotary_dim >> 1);
   float* scratch = sin_table + (rotary_dim >> 1);
   srb_launch_dependents();
@@ -677,54 +693,137 @@ proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qk
   }
   srb_grid_dependency_wait();
   const size_t src = (size_t)row * qkv_stride;
+  // entry `column` of the row: the tensor's, or the partial sums' added in part order
   auto value_at = [&](int column) -> float {
     if (num_parts == 0) return srb_to_float(qkv[src + column]);
     float x = 0.f;
     for (int part = 0; part < num_parts; ++part) x += qkv_parts[part * part_stride + src + column];
     return x;
   };
+  // eight entries from `column` on (EIGHT only); the loads of four parts are in flight together
+  auto eight_at = [&](int column, float* x) {
+    if (num_parts == 0) {
+      if (sizeof(T) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(qkv + src + column);
+        const __nv_bfloat162* pair = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(pair[j]); x[2 * j] = f.x; x[2 * j + 1] = f.y; }
+      } else {
+        const float4 lo = *reinterpret_cast<const float4*>(qkv + src + column), hi = *reinterpret_cast<const float4*>(qkv + src + column + 4);
+        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w; x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+      }
+      return;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = 0.f;
+    for (int first = 0; first < num_parts; first += 4) {
+      float4 lo[4], hi[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (first + j < num_parts) {
+          const float* from = qkv_parts + (first + j) * part_stride + src + column;
+          lo[j] = *reinterpret_cast<const float4*>(from);
+          hi[j] = *reinterpret_cast<const float4*>(from + 4);
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (first + j < num_parts) {
+          x[0] += lo[j].x; x[1] += lo[j].y; x[2] += lo[j].z; x[3] += lo[j].w;
+          x[4] += hi[j].x; x[5] += hi[j].y; x[6] += hi[j].z; x[7] += hi[j].w;
+        }
+    }
+  };
+  auto store_eight = [&](T* to, const float* x) {
+    if (sizeof(T) == 2) {
+      uint4 raw;
+      __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pair[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+      *reinterpret_cast<uint4*>(to) = raw;
+    } else {
+      *reinterpret_cast<float4*>(to) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(to + 4) = make_float4(x[4], x[5], x[6], x[7]);
+    }
+  };
+  // the whole row comes into shared memory in one round of loads: values and gate logits too, so that nothing waits for
+  // global memory a second time
   float sum_q = 0.f, sum_k = 0.f;
-  for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
-    const float x = value_at(i);
-    staged[i] = x;
-    if (i < q_width) sum_q = __fmaf_rn(x, x, sum_q); else sum_k = __fmaf_rn(x, x, sum_k);
+  if (EIGHT) {
+    for (int i = threadIdx.x * 8; i < q_width + k_width + v_width; i += blockDim.x * 8) {
+      float x[8];
+      eight_at(i, x);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { staged[i + j] = x[j]; sum = __fmaf_rn(x[j], x[j], sum); }
+      if (i < q_width) sum_q += sum; else if (i < q_width + k_width) sum_k += sum;
+    }
+    for (int i = q_width + k_width + v_width + threadIdx.x; i < row_width; i += blockDim.x) staged[i] = value_at(i);
+  } else {
+    for (int i = threadIdx.x; i < row_width; i += blockDim.x) {
+      const float x = value_at(i);
+      staged[i] = x;
+      if (i < q_width) sum_q = __fmaf_rn(x, x, sum_q); else if (i < q_width + k_width) sum_k = __fmaf_rn(x, x, sum_k);
+    }
   }
-  const float inv_q = q_weight ? 1.0f / sqrtf(srb_block_sum(sum_q, scratch) / (float)q_width + eps) : 1.f;
-  const float inv_k = k_weight ? 1.0f / sqrtf(srb_block_sum(sum_k, scratch) / (float)k_width + eps) : 1.f;
-  for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x) {
-    if (i < q_width) { if (q_weight) staged[i] = normed(staged[i], inv_q, q_weight[i]); }
-    else if (k_weight) staged[i] = normed(staged[i], inv_k, k_weight[i - q_width]);
+  const float2 sums = block_sum_pair(sum_q, sum_k, scratch);     // (its barrier also publishes the tables and the staged row)
+  const float inv_q = q_weight ? 1.0f / sqrtf(sums.x / (float)q_width + eps) : 1.f;
+  const float inv_k = k_weight ? 1.0f / sqrtf(sums.y / (float)k_width + eps) : 1.f;
+  // norm and rotation of a pair by the thread that owns it; entries behind the rotated ones are normed one by one
+  const int rest = head_dim - rotary_dim;
+  for (int item = threadIdx.x; item < (n_q + n_kv) * (half + rest); item += blockDim.x) {
+    const int head = item / (half + rest), i = item - head * (half + rest);
+    float* v = staged + (size_t)head * head_dim;
+    const float* w = head < n_q ? (q_weight ? q_weight + (size_t)head * head_dim : nullptr)
+                                : (k_weight ? k_weight + (size_t)(head - n_q) * head_dim : nullptr);
+    const float inv = head < n_q ? inv_q : inv_k;
+    if (i >= half) {
+      const int e = rotary_dim + (i - half);
+      if (w) v[e] = normed(v[e], inv, w[e]);
+      continue;
+    }
+    const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+    const float a = w ? normed(v[ia], inv, w[ia]) : v[ia], b = w ? normed(v[ib], inv, w[ib]) : v[ib];
+    const float cs = cos_table[i], sn = sin_table[i];
+    v[ia] = rotate_first(a, b, cs, sn);
+    v[ib] = rotate_second(a, b, cs, sn);
   }
   __syncthreads();
-  if (inv_freq) {
-    for (int item = threadIdx.x; item < (n_q + n_kv) * half; item += blockDim.x) {
-      const int head = item / half, i = item - head * half;
-      float* v = staged + (size_t)head * head_dim;
-      const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
-      const float a = v[ia], b = v[ib], cs = cos_table[i], sn = sin_table[i];
-      v[ia] = rotate_first(a, b, cs, sn);
-      v[ib] = rotate_second(a, b, cs, sn);
-    }
-    __syncthreads();
-  }
-  for (int i = threadIdx.x; i < q_width; i += blockDim.x) q_out[(size_t)row * q_width + i] = srb_from_float<T>(staged[i]);
   if (gate_out)
     for (int i = threadIdx.x; i < gate_cols; i += blockDim.x)
-      gate_out[(size_t)row * gate_cols + i] = 1.0f / (1.0f + expf(-value_at(q_width + k_width + n_kv * value_dim + i)));
-  if (!slots) return;
-  const int slot = slots[row];
-  if (slot < 0 || slot >= num_pages * page_size) {
-    if (threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+      gate_out[(size_t)row * gate_cols + i] = 1.0f / (1.0f + expf(-staged[q_width + k_width + v_width + i]));
+  int slot = -1;
+  if (slots) {
+    slot = slots[row];
+    if (slot < 0 || slot >= num_pages * page_size) {
+      if (threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+      slot = -1;
+    }
+  }
+  const size_t page = slot < 0 ? 0 : slot / page_size, inside = slot < 0 ? 0 : slot % page_size;
+  if (EIGHT) {
+    const int total = q_width + (slot < 0 ? 0 : k_width + v_width);
+    for (int i = threadIdx.x * 8; i < total; i += blockDim.x * 8) {
+      if (i < q_width) {
+        store_eight(q_out + (size_t)row * q_width + i, staged + i);
+      } else if (i < q_width + k_width) {
+        const int head = (i - q_width) / head_dim, e = (i - q_width) - head * head_dim;
+        store_eight(k_pool + ((page * n_kv + head) * page_size + inside) * head_dim + e, staged + i);
+      } else {
+        const int c = i - q_width - k_width, head = c / value_dim, e = c - head * value_dim;
+        store_eight(v_pool + ((page * n_kv + head) * page_size + inside) * value_dim + e, staged + i);
+      }
+    }
     return;
   }
-  const size_t page = slot / page_size, inside = slot % page_size;
+  for (int i = threadIdx.x; i < q_width; i += blockDim.x) q_out[(size_t)row * q_width + i] = srb_from_float<T>(staged[i]);
+  if (slot < 0) return;
   for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
     const int head = i / head_dim, e = i - head * head_dim;
     k_pool[((page * n_kv + head) * page_size + inside) * head_dim + e] = srb_from_float<T>(staged[q_width + i]);
   }
-  for (int i = threadIdx.x; i < n_kv * value_dim; i += blockDim.x) {
+  for (int i = threadIdx.x; i < v_width; i += blockDim.x) {
     const int head = i / value_dim, e = i - head * value_dim;
-    v_pool[((page * n_kv + head) * page_size + inside) * value_dim + e] = srb_from_float<T>(value_at(q_width + k_width + i));
+    v_pool[((page * n_kv + head) * page_size + inside) * value_dim + e] = srb_from_float<T>(staged[q_width + k_width + i]);
   }
 }
 
@@ -746,28 +845,32 @@ extern "C" int srb_proj_norm_rope_kv(const void* qkv, const float* qkv_parts, in
     SRB_FAIL("proj_norm_rope_kv: rows of the projection are narrower than their parts together");
   if (gate_cols > 0 && !gate_out) SRB_FAIL("proj_norm_rope_kv: gate logits without a place for the gates");
   if (!(eps >= 0.f)) SRB_FAIL("proj_norm_rope_kv: eps must be finite and non-negative");
-  const size_t smem = ((size_t)(n_q + n_kv) * head_dim + rotary_dim + 33) * sizeof(float);
+  const size_t smem = ((size_t)(n_q + n_kv) * head_dim + (size_t)n_kv * value_dim + gate_cols + 4 + rotary_dim + 66) * sizeof(float);
   if (smem > 227 * 1024) SRB_FAIL("proj_norm_rope_kv: %zu bytes of shared memory exceed 232448", smem);
   cudaStream_t s = (cudaStream_t)stream;
+  const bool eight = head_dim % 8 == 0 && value_dim % 8 == 0 && qkv_stride % 8 == 0 && part_stride % 4 == 0 &&
+                     (((uintptr_t)qkv | (uintptr_t)qkv_parts | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
+  // few rows: more threads per row would idle; many rows: 256 threads keep the loads of a row in flight together
+  const long long columns = (long long)(n_q + n_kv) * head_dim + (long long)n_kv * value_dim;
+  const int threads = rows <= 64 && columns >= 2048 ? 512 : (columns >= 2048 ? 256 : 128);
+#define SRB_PROJ_LAUNCH(T, EIGHT)                                                                                              \
+  do {                                                                                                                         \
+    if (smem > 48 * 1024)                                                                                                      \
+      SRB_CUDA_CALL(cudaFuncSetAttribute(proj_norm_rope_kv_kernel<T, EIGHT>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                         (int)smem));                                                                          \
+    SRB_CUDA_CALL(srb_launch(proj_norm_rope_kv_kernel<T, EIGHT>, dim3(rows), dim3(threads), smem, s, (const T*)qkv, qkv_parts, \
+                             num_parts, (size_t)part_stride, qkv_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, gate_out,          \
+                             positions, slots, q_weight, k_weight, eps, inv_freq, rotary_dim, interleaved, magnitude, n_q,     \
+                             n_kv, head_dim, value_dim, gate_cols, page_size, num_pages, error_word));                         \
+  } while (0)
   if (dtype == SRB_DTYPE_F32) {
-    if (smem > 48 * 1024)
-      SRB_CUDA_CALL(cudaFuncSetAttribute(proj_norm_rope_kv_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    SRB_CUDA_CALL(srb_launch(proj_norm_rope_kv_kernel<float>, dim3(rows), dim3(256), smem, s, (const float*)qkv, qkv_parts,
-                             num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool,
-                             gate_out, positions, slots, q_weight, k_weight, eps, inv_freq, rotary_dim, interleaved,
-                             magnitude, n_q, n_kv, head_dim, value_dim, gate_cols, page_size, num_pages, error_word));
+    if (eight) SRB_PROJ_LAUNCH(float, true); else SRB_PROJ_LAUNCH(float, false);
   } else if (dtype == SRB_DTYPE_BF16) {
-    if (smem > 48 * 1024)
-      SRB_CUDA_CALL(cudaFuncSetAttribute(proj_norm_rope_kv_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem));
-    SRB_CUDA_CALL(srb_launch(proj_norm_rope_kv_kernel<__nv_bfloat16>, dim3(rows), dim3(256), smem, s,
-                             (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
-                             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, gate_out, positions, slots,
-                             q_weight, k_weight, eps, inv_freq, rotary_dim, interleaved, magnitude, n_q, n_kv, head_dim,
-                             value_dim, gate_cols, page_size, num_pages, error_word));
+    if (eight) SRB_PROJ_LAUNCH(__nv_bfloat16, true); else SRB_PROJ_LAUNCH(__nv_bfloat16, false);
   } else {
     SRB_FAIL("proj_norm_rope_kv: unknown dtype %d", dtype);
   }
+#undef SRB_PROJ_LAUNCH
   SRB_LAUNCH_CHECK("proj_norm_rope_kv");
   return SRB_OK;
 }
