@@ -7,11 +7,12 @@
 //                        key/value latent and rotation of the shared key part -> the row's cache slot
 //   srb_rope_slice       rotates a slice of every head of a [rows, heads, *] tensor into another tensor
 //   srb_head_linear      out[r, h, :] = W_h x[r, h, :] for every head h (one weight matrix per head), with
-//                        an optional sigmoid gate per (row, head) on the result
+//                        an optional sigmoid gate per (row, head) or per (row, head, entry) on the result
 //
 // Norms, angles and the rotation are 32-bit; T is the storage type (float or bfloat16).  The rotation
-// pairs entry i with entry i + dims/2 of the slice ("rotate half"): (u, v) -> (u cos a - v sin a,
-// v cos a + u sin a), a = position * inv_freq[i]; entries of the slice behind `rotary_dim` pass unchanged.
+// pairs entry i with entry i + dims/2 of the slice ("rotate half") or, with `interleaved`, entry 2i with entry 2i + 1:
+// (u, v) -> (u cos a - v sin a, v cos a + u sin a), a = position * inv_freq[i], cosines and sines times `magnitude`;
+// entries of the slice behind `rotary_dim` pass unchanged.
 #include "common.cuh"
 #include "tile_mma.cuh"
 #include <math.h>

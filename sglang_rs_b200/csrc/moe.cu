@@ -11,6 +11,11 @@
 //   srb_moe_down      y[slot, :]   = W_down[e] act[slot]                              (32-bit result)
 //   srb_moe_combine   out[row, :]  = sum over the row's choices, in their order, of weight * y[slot]   (32-bit)
 //
+// The router may have more outputs than there are experts with matrices (srb_moe_route / srb_moe_select are then called
+// with the number of outputs, srb_moe_plan and the products with the number of experts): a choice beyond the experts gets
+// no slot, the products never see it, and srb_moe_combine_identity adds weight * h[row] for it: an expert that returns
+// its input.
+//
 // Nothing here is decided on the host: counts, offsets and tiles stay on the device, the products are
 // launched for the largest number of tiles the step can need, and blocks without a tile leave at once.
 // Every output element is accumulated in 32-bit over the inner index in order by one thread, so a row's

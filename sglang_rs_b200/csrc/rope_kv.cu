@@ -11,6 +11,9 @@
 // that covers every encoding of the rotary family without a change here.
 //
 // Page pool layout: [page, kv_head, slot_in_page, head_dim].
+//
+// srb_proj_norm_rope_kv (at the end) is the same step for a mixer that norms q and k over the whole projection, keeps
+// values of their own width and reads the logits of an output gate from the same product.
 #include "common.cuh"
 #include "mma_helpers.cuh"
 #include <algorithm>
@@ -733,7 +736,9 @@ proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qk
         }
     }
   };
-  auto store_eight = [&](T* to, const float* x) {
+  auto store_eight = [&](T* to, const float* from) {       // `from`: shared memory, on a 16-byte border
+    const float4 lo = *reinterpret_cast<const float4*>(from), hi = *reinterpret_cast<const float4*>(from + 4);
+    const float x[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     if (sizeof(T) == 2) {
       uint4 raw;
       __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&raw);
@@ -754,7 +759,9 @@ proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qk
       eight_at(i, x);
       float sum = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { staged[i + j] = x[j]; sum = __fmaf_rn(x[j], x[j], sum); }
+      for (int j = 0; j < 8; ++j) sum = __fmaf_rn(x[j], x[j], sum);
+      *reinterpret_cast<float4*>(staged + i) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(staged + i + 4) = make_float4(x[4], x[5], x[6], x[7]);
       if (i < q_width) sum_q += sum; else if (i < q_width + k_width) sum_k += sum;
     }
     for (int i = q_width + k_width + v_width + threadIdx.x; i < row_width; i += blockDim.x) staged[i] = value_at(i);
@@ -769,23 +776,23 @@ proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qk
   const float inv_q = q_weight ? 1.0f / sqrtf(sums.x / (float)q_width + eps) : 1.f;
   const float inv_k = k_weight ? 1.0f / sqrtf(sums.y / (float)k_width + eps) : 1.f;
   // norm and rotation of a pair by the thread that owns it; entries behind the rotated ones are normed one by one
+  // (a warp per head and a lane per pair: no division in the loop)
   const int rest = head_dim - rotary_dim;
-  for (int item = threadIdx.x; item < (n_q + n_kv) * (half + rest); item += blockDim.x) {
-    const int head = item / (half + rest), i = item - head * (half + rest);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int head = warp; head < n_q + n_kv; head += warps) {
     float* v = staged + (size_t)head * head_dim;
     const float* w = head < n_q ? (q_weight ? q_weight + (size_t)head * head_dim : nullptr)
                                 : (k_weight ? k_weight + (size_t)(head - n_q) * head_dim : nullptr);
     const float inv = head < n_q ? inv_q : inv_k;
-    if (i >= half) {
-      const int e = rotary_dim + (i - half);
-      if (w) v[e] = normed(v[e], inv, w[e]);
-      continue;
+    for (int i = lane; i < half; i += 32) {
+      const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+      const float a = w ? normed(v[ia], inv, w[ia]) : v[ia], b = w ? normed(v[ib], inv, w[ib]) : v[ib];
+      const float cs = cos_table[i], sn = sin_table[i];
+      v[ia] = rotate_first(a, b, cs, sn);
+      v[ib] = rotate_second(a, b, cs, sn);
     }
-    const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
-    const float a = w ? normed(v[ia], inv, w[ia]) : v[ia], b = w ? normed(v[ib], inv, w[ib]) : v[ib];
-    const float cs = cos_table[i], sn = sin_table[i];
-    v[ia] = rotate_first(a, b, cs, sn);
-    v[ib] = rotate_second(a, b, cs, sn);
+    if (w)
+      for (int e = rotary_dim + lane; e < head_dim; e += 32) v[e] = normed(v[e], inv, w[e]);
   }
   __syncthreads();
   if (gate_out)
