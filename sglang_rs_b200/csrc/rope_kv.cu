@@ -750,7 +750,7 @@ proj_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qk
       *reinterpret_cast<float4*>(to + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
   };
-  // the whole row comes into shared memory in one round of loads: values and gate logits too, so that nothing waits for
+  // the whole row comes into shared memory in one sweep of loads: values and gate logits too, so that nothing waits for
   // global memory a second time
   float sum_q = 0.f, sum_k = 0.f;
   if (EIGHT) {

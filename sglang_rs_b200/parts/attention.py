@@ -66,9 +66,6 @@ class GroupedQueryAttention(Mixer):
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         if not 0 < head_dim <= self.MAX_HEAD_DIM:
             raise ValueError(f"head_dim {head_dim} is outside what the attention kernels take (1 to {self.MAX_HEAD_DIM})")
-        if num_heads // num_kv_heads > self.MAX_HEADS_PER_KV_HEAD:
-            raise ValueError(f"{num_heads // num_kv_heads} query heads per kv head exceed the "
-                             f"{self.MAX_HEADS_PER_KV_HEAD} that the attention kernels take")
         self.hidden, self.n_q, self.n_kv, self.d = int(hidden), int(num_heads), int(num_kv_heads), int(head_dim)
         self.scale, self.position, self.names = float(scale), position, names
         self.qk_norm_eps, self.window = qk_norm_eps, window
@@ -86,6 +83,11 @@ class GroupedQueryAttention(Mixer):
         self.partial_sums = bool(partial_sums)
         #: the arrangement that ``ops.proj_norm_rope_kv`` prepares
         self.wide = self.whole_norm or self.vd != self.d or self.sink is not None or names.gate is not None
+        if not self.wide and num_heads // num_kv_heads > self.MAX_HEADS_PER_KV_HEAD:
+            # (the fused per-head kernel's limit; the other arrangement goes through kernels that take the heads of a kv
+            # head in chunks)
+            raise ValueError(f"{num_heads // num_kv_heads} query heads per kv head exceed the "
+                             f"{self.MAX_HEADS_PER_KV_HEAD} that the attention kernels take")
         if self.wide and (self.values_from_keys or names.q_bias or names.k_bias or names.v_bias):
             raise ValueError("norms over whole projections, values of their own width, a sink and a gate are not built "
                              "together with biases or with values that are the keys")

@@ -121,7 +121,7 @@ def paged(keys, values, page, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv,d,vd,window,split", [(4, 2, 16, 8, 24, 0), (3, 1, 10, 14, 0, 32), (34, 2, 8, 12, 70, 64),
+@pytest.mark.parametrize("heads,kv,d,vd,window,split", [(4, 2, 16, 8, 24, 0), (3, 1, 10, 14, 0, 32), (34, 1, 8, 12, 70, 64),
                                                         (2, 2, 20, 20, 1, 0)])
 def test_attention_with_a_unit_sink_gates_and_values_of_their_own_width(dtype, heads, kv, d, vd, window, split):
     """The generic kernel: a sink in the denominator (once, also when the keys are split), a gate per (row, head), values

@@ -83,15 +83,16 @@ SMALL_C = config(36, 50, [
     layer(attention(2, 1, 6, 10, window=33, rot_dims=2), None),
 ], loop=(0, 1, 2), scale=0.8)
 #: sizes that the tensor-core kernels of the bfloat16 path take: heads of 64 with values as wide, latent rows of 80
-#: entries; 34 query heads on 2 kv heads go in chunks of the generic kernel in 32-bit
+#: entries
 SMALL_D = config(64, 90, [
     layer(attention(4, 2, 64, 64, window=48, rot_dims=32), moe(6, 2, 48, identity=2, shared=32)),
     layer(latent(5, 16, 16, 24, 32, 64), dense(96)),
     layer(attention(2, 1, 64, 64, window=150), None),
 ], loop=(0, 2, 2), scale=1.3)
-#: a stretch that is "walked" once (no pass is opened), values wider than keys, many heads per kv head
+#: a stretch that is "walked" once (no pass is opened), values wider than keys, 34 query heads on one kv head (two chunks
+#: of the generic kernel)
 SMALL_E = config(40, 60, [
-    layer(attention(34, 2, 8, 12, window=20, rot_dims=4), moe(2, 2, 16, identity=6)),
+    layer(attention(34, 1, 8, 12, window=20, rot_dims=4), moe(2, 2, 16, identity=6)),
     layer(latent(2, 8, 8, 8, 16, 16), moe(3, 2, 16, shared=8)),
 ], loop=(0, 2, 1), scale=2.0)
 
