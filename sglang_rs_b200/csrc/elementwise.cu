@@ -348,7 +348,7 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
                                      const float* __restrict__ delta_f32, NormSpec inner, NormSpec outer,
                                      T* __restrict__ out, size_t out_pitch, const float* __restrict__ extra,
                                      const int* __restrict__ row_index, int width, int write_residual,
-                                     const float* __restrict__ addend) {
+                                     const float* __restrict__ addend, int num_parts, size_t part_stride) {
   extern __shared__ float staged[];          // width floats, then 33 floats of scratch
   float* scratch = staged + width;
   srb_launch_dependents();
@@ -357,8 +357,25 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
   const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
   const bool pending = delta || delta_f32;
   if (pending) {
-    for (int i = threadIdx.x; i < width; i += blockDim.x)
-      staged[i] = delta ? srb_to_float(delta[src + i]) : delta_f32[src + i];
+    if (num_parts > 0) {
+      // partial sums of a product cut along K, added in part order
+      for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float sum = 0.f;
+        for (int first = 0; first < num_parts; first += 4) {       // four loads in flight
+          float d[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (first + j < num_parts) d[j] = delta_f32[(first + j) * part_stride + src + i];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (first + j < num_parts) sum += d[j];
+        }
+        staged[i] = sum;
+      }
+    } else {
+      for (int i = threadIdx.x; i < width; i += blockDim.x)
+        staged[i] = delta ? srb_to_float(delta[src + i]) : delta_f32[src + i];
+    }
     __syncthreads();
     norm_in_place(staged, width, inner, scratch);
   }
@@ -380,13 +397,16 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
 
 // `*_groups` (RMS norms only; 1: the whole row) and `*_scale` (1: none) as NormSpec says.  `addend` (optional, float,
 // shaped like the residual): a second term of the sum, added after the pending one: x = residual + inner(delta) + addend.
-extern "C" int srb_norm_add_norm_plus(float* residual, const void* delta, const float* delta_f32, int inner_kind,
+// `num_parts` > 0: `delta_f32` holds that many partial sums of the pending term, `part_stride` floats apart, which are
+// added in part order before the inner norm.
+extern "C" int srb_norm_add_norm_parts(float* residual, const void* delta, const float* delta_f32, int inner_kind,
                                     const float* inner_weight, const float* inner_bias, float inner_eps, int inner_groups,
                                     float inner_scale, int outer_kind, const float* outer_weight, const float* outer_bias,
                                     float outer_eps, int outer_groups, float outer_scale, void* out, long long out_pitch,
                                     const float* extra, const int* row_index, int rows, int width, int write_residual,
-                                    int dtype, const float* addend, void* stream) {
+                                    int dtype, const float* addend, int num_parts, long long part_stride, void* stream) {
   if (rows <= 0) return SRB_OK;
+  if (num_parts < 0 || (num_parts > 0 && (!delta_f32 || delta))) SRB_FAIL("norm_add_norm: partial sums come as float and alone");
   for (int groups : {inner_groups, outer_groups})
     if (groups < 1 || width % groups) SRB_FAIL("norm_add_norm: a row of %d entries does not split into %d equal parts", width, groups);
   if ((inner_groups > 1 && inner_kind != SRB_NORM_RMS) || (outer_groups > 1 && outer_kind != SRB_NORM_RMS))
@@ -409,14 +429,14 @@ extern "C" int srb_norm_add_norm_plus(float* residual, const void* delta, const 
       SRB_CUDA_CALL(cudaFuncSetAttribute(norm_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SRB_CUDA_CALL(srb_launch(norm_add_norm_kernel<float>, dim3(rows), dim3(block), smem, s, residual, (const float*)delta,
                              delta_f32, inner, outer, (float*)out, (size_t)out_pitch, extra, row_index, width,
-                             write_residual, addend));
+                             write_residual, addend, num_parts, (size_t)part_stride));
   } else if (dtype == SRB_DTYPE_BF16) {
     if (smem > 48 * 1024)
       SRB_CUDA_CALL(cudaFuncSetAttribute(norm_add_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
     SRB_CUDA_CALL(srb_launch(norm_add_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(block), smem, s, residual,
                              (const __nv_bfloat16*)delta, delta_f32, inner, outer, (__nv_bfloat16*)out, (size_t)out_pitch,
-                             extra, row_index, width, write_residual, addend));
+                             extra, row_index, width, write_residual, addend, num_parts, (size_t)part_stride));
   } else {
     SRB_FAIL("norm_add_norm: unknown dtype %d", dtype);
   }
@@ -430,9 +450,9 @@ extern "C" int srb_norm_add_norm_ex(float* residual, const void* delta, const fl
                                     float outer_eps, int outer_groups, float outer_scale, void* out, long long out_pitch,
                                     const float* extra, const int* row_index, int rows, int width, int write_residual,
                                     int dtype, void* stream) {
-  return srb_norm_add_norm_plus(residual, delta, delta_f32, inner_kind, inner_weight, inner_bias, inner_eps, inner_groups,
-                                inner_scale, outer_kind, outer_weight, outer_bias, outer_eps, outer_groups, outer_scale, out,
-                                out_pitch, extra, row_index, rows, width, write_residual, dtype, nullptr, stream);
+  return srb_norm_add_norm_parts(residual, delta, delta_f32, inner_kind, inner_weight, inner_bias, inner_eps, inner_groups,
+                                 inner_scale, outer_kind, outer_weight, outer_bias, outer_eps, outer_groups, outer_scale, out,
+                                 out_pitch, extra, row_index, rows, width, write_residual, dtype, nullptr, 0, 0, stream);
 }
 
 extern "C" int srb_norm_add_norm(float* residual, const void* delta, const float* delta_f32, int inner_kind,

@@ -88,21 +88,20 @@ def _build(config: TitatarConfig) -> DecoderModel:
                 width, m.heads, m.kv_heads, m.dim, m.scale, rotation(m.rot, m.dim, False) or NoPositionEncoding(),
                 AttentionNames(q=p + "mix.q", k=p + "mix.k", v=p + "mix.v", o=p + "mix.o", q_norm=p + "mix.q.norm",
                                k_norm=p + "mix.k.norm", gate=p + "mix.g"),
-                qk_norm_eps=eps, window=m.window, whole_norm=True, value_dim=m.vdim, sink=WINDOWED_SINK, partial_sums=False)
+                qk_norm_eps=eps, window=m.window, whole_norm=True, value_dim=m.vdim, sink=WINDOWED_SINK)
         else:
             mixer = LatentAttention(
                 width, m.heads, m.dim, m.rot_dim, m.vdim, m.q_rank, m.kv_rank, m.scale, eps, rotation(m.rot, m.rot_dim, True),
                 LatentAttentionNames(q_down=p + "mix.dq", q_norm=p + "mix.dq.norm", q_up=p + "mix.uq", kv_down=p + "mix.dkv",
                                      kv_norm=p + "mix.dkv.norm", k_up=p + "mix.uk", v_up=p + "mix.uv", o=p + "mix.o",
                                      sink=p + "mix.sink", gate=p + "mix.g"),
-                gate_per_entry=True)
+                gate_per_entry=True, partial_sums=True)
         f = spec.mlp
         if f is None:
             layers.append(SandwichBlock(norm(p + "norm1"), mixer, norm(p + "norm1b")))
             continue
         if isinstance(f, DenseSizes):
-            feed_forward = GatedMlp(width, f.ff, "silu", GatedMlpNames(gate=p + "mlp.gate", up=p + "mlp.up", down=p + "mlp.down"),
-                                    partial_sums=False)
+            feed_forward = GatedMlp(width, f.ff, "silu", GatedMlpNames(gate=p + "mlp.gate", up=p + "mlp.up", down=p + "mlp.down"))
         else:
             shared = None
             if f.shared_ff:

@@ -213,6 +213,8 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
                   extra: Optional[torch.Tensor] = None, addend: Optional[torch.Tensor] = None) -> None:
     """x = residual + inner(delta) (+ addend); residual = x if asked; out = outer(x), all sums and means in 32-bit.
     ``addend`` (float32, shaped like the residual) is a second term of the sum, added after the pending one.
+    ``delta`` may also be float32 [parts, rows, width]: partial sums of a product cut along K, added in part order
+    before the inner norm.
 
     ``inner`` and ``outer`` are ``(kind, weight, bias, eps)`` with kind one of ``NORM_KINDS`` (``none``: the
     identity; ``rms``: v / sqrt(mean(v^2) + eps) * w; ``layer``: (v - mean) / sqrt(var + eps) * w + b) or None
@@ -238,11 +240,17 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
     inner_kind, inner_w, inner_b, inner_eps, inner_groups, inner_scale = spec(inner)
     outer_kind, outer_w, outer_b, outer_eps, outer_groups, outer_scale = spec(outer)
     whole = as_float = None
+    num_parts = part_stride = 0
     if delta is not None:
         _need(delta, "delta")
-        if delta.shape != residual.shape:
+        if delta.dim() == 3:
+            _need(delta, "delta", torch.float32)
+            if delta.shape[1:] != residual.shape:
+                raise KernelError("norm_add_norm: partial sums and residual differ in shape")
+            as_float, num_parts, part_stride = delta, delta.shape[0], delta.stride(0)
+        elif delta.shape != residual.shape:
             raise KernelError("norm_add_norm: delta and residual differ in shape")
-        if delta.dtype == torch.float32 and (out is None or out.dtype != torch.float32):
+        elif delta.dtype == torch.float32 and (out is None or out.dtype != torch.float32):
             as_float = delta
         else:
             whole = delta
@@ -270,11 +278,12 @@ def norm_add_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], inner, 
     if row_index is not None:
         _need(row_index, "row_index", torch.int32)
     lib = load_library("elementwise")
-    _check(lib, lib.srb_norm_add_norm_plus(
+    _check(lib, lib.srb_norm_add_norm_parts(
         _ptr(residual), _ptr(whole), _ptr(as_float), inner_kind, _ptr(inner_w), _ptr(inner_b), ctypes.c_float(inner_eps),
         inner_groups, ctypes.c_float(inner_scale), outer_kind, _ptr(outer_w), _ptr(outer_b), ctypes.c_float(outer_eps),
         outer_groups, ctypes.c_float(outer_scale), _ptr(out), ctypes.c_longlong(pitch),
-        _ptr(extra), _ptr(row_index), rows, width, int(write_residual), dtype_code(dtype), _ptr(addend), _stream()))
+        _ptr(extra), _ptr(row_index), rows, width, int(write_residual), dtype_code(dtype), _ptr(addend), num_parts,
+        ctypes.c_longlong(part_stride), _stream()))
 
 
 #: activations of a gated feed-forward, act(gate) * up, by the numbers of csrc/activations.cuh

@@ -59,7 +59,8 @@ class LatentAttention(Mixer):
 
     def __init__(self, hidden: int, num_heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int,
                  scale: float, eps: float, rotary: Optional[RotaryEncoding], names: LatentAttentionNames, *,
-                 window: Optional[int] = None, cache_window: Optional[int] = -1, gate_per_entry: bool = False):
+                 window: Optional[int] = None, cache_window: Optional[int] = -1, gate_per_entry: bool = False,
+                 partial_sums: bool = False):
         """``rotary``: the rotation of the rot_dim part (its ``rotary_dim`` leading entries are rotated, the rest
         pass unchanged); None leaves it alone.  ``names.sink`` / ``names.gate`` None: no sink / no gate.
         ``cache_window`` -1: the layer's own window."""
@@ -82,6 +83,8 @@ class LatentAttention(Mixer):
         if rot_dim < 0 or (rotary is not None and rotary.rotary_dim > rot_dim):
             raise ValueError(f"latent attention: the rotation covers more than the {rot_dim} rotated entries")
         self.gate_per_entry = bool(gate_per_entry)
+        #: whether the output product may hand on partial sums along K (for a consumer that adds them in order)
+        self.partial_sums = bool(partial_sums)
         if kv_rank > 1024:
             raise ValueError(f"latent attention: a latent of {kv_rank} entries exceeds the 1024 the attention kernel takes")
         self.hidden, self.heads, self.dim, self.rot_dim, self.vdim = int(hidden), int(num_heads), int(dim), int(rot_dim), int(value_dim)
@@ -188,4 +191,4 @@ class LatentAttention(Mixer):
         out = torch.empty((rows, h, self.vdim), dtype=x.dtype, device=x.device)
         gate = proj[:, q_cols + kv_cols:] if self.names.gate else None
         ops.head_linear(mixed, self.w_uv, out, gate=gate, gate_per_entry=self.gate_per_entry)
-        return ops.linear(out.view(rows, h * self.vdim), self.w_o, error_word=ctx.error_word)
+        return ops.linear(out.view(rows, h * self.vdim), self.w_o, error_word=ctx.error_word, partial_ok=self.partial_sums)

@@ -58,6 +58,13 @@ def test_norm_with_weights_around_zero_and_a_second_term_of_the_sum(dtype):
     residual = x.to(DEV)
     PassSum().forward(None, residual, None, x0.to(DEV), 1)
     close(residual, (x + x0).double().numpy(), torch.float32, "stream + embedding output", 1e-7)
+    # the pending term as partial sums of a product cut along K: added in order, then normed
+    pieces = torch.randn(5, rows, width, generator=g)
+    residual = x.to(DEV)
+    out = ahead.add_norm(residual, NormedDelta(pieces.to(DEV), behind), dtype)
+    total = x.double().numpy() + pt.norm_one_plus(pieces.double().sum(0).numpy(), stored["b"].double().numpy(), eps)
+    close(residual, total, torch.float32, "the stream after the normed sum of the parts", 1e-6)
+    close(out, pt.norm_one_plus(total, stored["a"].double().numpy(), eps), dtype, "norm of that sum")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
