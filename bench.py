@@ -915,9 +915,9 @@ def titatar_layers(count: int):
     wavelengths; a dense feed-forward of three widths in the first layer, then 64 experts of 1,408 with 6 chosen among
     them and 8 router outputs without tensors, beside a shared expert of 2,816."""
     windowed = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 1.0 / math.sqrt(128), "mask": {"size": 1024},
-                "rot": {"base": 1000000.0, "dims": 64}}
+                "rot": {"base": 500000.0, "dims": 64}}
     through_latents = {**GEGEPEL_MIXER, "rot": {"base": 10000.0, "dims": 64,
-                                                "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+                                                "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
     experts = {"kind": "moe", "router": {"experts": 64, "top": 6, "identity": 8}, "expert": {"ff": 1408}, "shared": {"ff": 2816}}
     pattern = [("attention", windowed, {"kind": "dense", "ff": 3 * GEGEPEL_WIDTH}), ("attention", windowed, experts),
                ("latent_attention", through_latents, experts), ("latent_attention", through_latents, experts)]
